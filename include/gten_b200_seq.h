@@ -1,0 +1,108 @@
+/* gten_b200_seq.h -- C-ABI of libgten_b200_seq.so: layer-list sequence models on one B200 (sm_100a).
+ *
+ * The hot path of include/gten_b200.h is one fixed graph (TinyLlama) with the reference's quantised arithmetic.  This
+ * library runs models that are DESCRIBED: a list of layers, each a parallel block (one norm, a token mixer made of
+ * weighted branches, an optional gated feed-forward, both fed through a short causal convolution of the normalised
+ * stream), an optional weight-shared loop over a range of layers, an optional hashed bigram embedding.  Weights are
+ * bfloat16; the compute mode is bfloat16 operands with fp32 accumulation (tensor cores) or true fp32.
+ *
+ * It shares the context, the stream, the allocator and the error convention with gten_b200.h (the gtb_* calls of that
+ * header are exported by this library as well): 0 on success, a message in gtb_last_error() otherwise.
+ *
+ * State lives in SLOTS, like the batched decode of gtb_engine_batch_*: a slot owns one sequence's position, previous
+ * token, per-layer-run K/V cache, recurrent state and convolution history.  A STEP feeds any number of segments
+ * (slot, next tokens) in one pass over the weights; the rows of all segments share every matrix product.
+ */
+#ifndef GTEN_B200_SEQ_H
+#define GTEN_B200_SEQ_H
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum { GTB_SEQ_BF16 = 0, GTB_SEQ_F32 = 1 };                       /* compute mode */
+enum { GTB_MIX_SIGMOID_ATTN = 1, GTB_MIX_RETENTION = 2 };         /* branch kinds of a token mixer */
+
+/* One branch of a token mixer.  Tensors of branch b of layer i are "l<i>.mix.<name>.{q,k,v,o,...}".
+ *  GTB_MIX_SIGMOID_ATTN: causal attention over the slot's K/V cache, `heads` query heads sharing `kv_heads` key/value
+ *    heads in consecutive groups; weight of key j = sigmoid(scale * q.k_j + pb[head]), no normalisation over keys;
+ *    qk_norm: q and k scaled to unit RMS per head (eps of the model).  Tensors q, k, v, pb, o.
+ *  GTB_MIX_RETENTION: S <- decay[head] * S + k v^T, o = S^T q per head (fp32 state per slot); rotary positions on the
+ *    first rot_dims dimensions of q and k (pairs i, i + rot_dims/2, angle pos * rot_base^(-2i/rot_dims)); k multiplied
+ *    by `scale` after rotation; out_norm: o scaled to unit RMS per head; gated: o *= silu(g h).  Tensors q, k, v, g, o. */
+typedef struct {
+    int kind;
+    char name[16];
+    int heads, kv_heads, dim, vdim;
+    float scale;
+    int qk_norm;
+    int rot_dims;
+    float rot_base;
+    int out_norm, gated;
+    float out_scale;                 /* weight of this branch in the mixer's sum */
+    const float* decay;              /* [heads], host; copied */
+} gtb_seq_branch;
+
+typedef struct {
+    int n_branches;                  /* 1 or 2 */
+    gtb_seq_branch branch[2];
+    int ff;                          /* 0: no feed-forward; else W_down(gelu_tanh(W_gate h) * (W_up h)) */
+} gtb_seq_layer;
+
+typedef struct {
+    int vocab, width, n_layers;
+    float eps;
+    int taps;                        /* causal per-channel convolution in front of each sublayer; 0: none */
+    int bigram_buckets, bigram_mul_prev, bigram_mul_cur;   /* buckets = 0: no bigram table */
+    int loop_start, loop_stop, loop_times;                 /* times = 0: no loop */
+    int mode;                        /* GTB_SEQ_BF16 / GTB_SEQ_F32 */
+    int n_slots, max_ctx;            /* sequences held at once; positions per slot */
+    int max_rows;                    /* rows per pass over the weights (longer steps are cut into passes); 0: default */
+} gtb_seq_config;
+
+typedef struct gtb_seq_model* gtb_seq_t;
+
+int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_layer* layers);
+int gtb_seq_destroy(gtb_seq_t m);
+/* one tensor of the checkpoint by its name; bf16 (dtype 0) or int32/fp32 payloads are not needed by this family.
+ * shape is checked against the description */
+int gtb_seq_set_tensor(gtb_seq_t m, const char* name, const void* h_bf16, const int64_t* shape, int ndim);
+int gtb_seq_finalize(gtb_seq_t m);                                 /* fails and names the first tensor that is missing */
+int gtb_seq_n_runs(gtb_seq_t m, int* n);                           /* layer runs per token (a looped layer counts each pass) */
+
+/* slots */
+int gtb_seq_slot_reset(gtb_seq_t m, int slot);                     /* empty sequence: position 0, zero state */
+int gtb_seq_slot_position(gtb_seq_t m, int slot, int* pos);
+
+/* The step function.  Segment s feeds seg_len[s] tokens (consecutive in h_tokens) to slot seg_slot[s], continuing from the
+ * slot's state; a slot appears at most once.  want_rows: indices into the step's rows (0 .. sum(seg_len)-1, ascending) whose
+ * logits are written to h_logits [n_want][vocab] (may be 0).  Rows beyond max_rows are run as further passes. */
+int gtb_seq_step(gtb_seq_t m, int n_seg, const int32_t* seg_slot, const int32_t* seg_len, const int32_t* h_tokens,
+                 int n_want, const int32_t* want_rows, float* h_logits);
+/* same, and the last row of every segment is sampled greedily on the device (first maximum): h_next [n_seg] */
+int gtb_seq_step_greedy(gtb_seq_t m, int n_seg, const int32_t* seg_slot, const int32_t* seg_len, const int32_t* h_tokens,
+                        int32_t* h_next);
+/* n greedy steps of the given slots without a host round trip: each slot feeds its last sampled token (set by
+ * gtb_seq_step_greedy or a previous call); tokens land in h_out [n_slots_in][n_steps].  A slot that samples eos_id (>= 0)
+ * keeps repeating it and its state stops advancing. */
+int gtb_seq_decode(gtb_seq_t m, int n, const int32_t* slots, int n_steps, int eos_id, int32_t* h_out);
+/* the k (<= 64) largest logits of segment s's last row of the last step, largest first, ties to the lower id */
+int gtb_seq_topk(gtb_seq_t m, int seg, int k, float* h_values, int32_t* h_ids);
+/* logits of segment s's last row of the last gtb_seq_step_greedy / gtb_seq_decode call */
+int gtb_seq_last_logits(gtb_seq_t m, int seg, float* h_logits);
+
+/* options: "capture" (1: the residual stream after every layer run of the last pass is kept for gtb_seq_read_capture),
+ * "tensor" (1, default: bf16 matrix products of >= "tensor_min_rows" rows on tcgen05; 0: SIMT kernels only),
+ * "tensor_min_rows" (default 64), "graph" (1, default: gtb_seq_decode replays a CUDA graph per step),
+ * "fused_attn" (1, default: tensor-core prefill kernels for the mixers where shapes allow; 0: the simple kernels) */
+int gtb_seq_set_option(gtb_seq_t m, const char* name, int value);
+int gtb_seq_read_capture(gtb_seq_t m, int run, int row, float* h_out);    /* [width] */
+int gtb_seq_weight_bytes(gtb_seq_t m, size_t* nbytes);
+int gtb_seq_state_bytes_per_slot(gtb_seq_t m, size_t* nbytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GTEN_B200_SEQ_H */

@@ -1,0 +1,759 @@
+// gtb_seq.cu -- host side of libgten_b200_seq.so (include/gten_b200_seq.h): model description, weight placement, slot state,
+// the step function (one pass over the weights for the rows of any number of segments), greedy decode loop, top-k.
+//
+// Layout decisions:
+//  * per layer THREE matrix products: [all branch projections] <- operand A (h + conv_a(h)); [gate | up] <- operand B (h + conv_b(h));
+//    x += [branch outputs (already weighted) | gelu(gate) * up] . [o_0 | o_1 | down]^T  -- the branch out-projections and the down
+//    projection are concatenated along K, so the residual update is ONE product that accumulates into the fp32 stream.
+//  * every operand / weight row is zero-padded to a multiple of 64 elements (one tensor-core k-block, 16-byte aligned rows).
+//  * a looped layer has one set of weights and one set of state (cache, recurrent state, conv history) per pass: a "run".
+#include <math.h>
+#include <string.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/gten_b200_seq.h"
+#include "gtb_internal.h"
+#include "gtb_sample.cuh"
+#include "gtb_seq_gemm.h"
+#include "gtb_seq_kernels.cuh"
+
+using namespace gtb;
+using namespace gtb::seq;
+
+namespace {
+
+inline int pad64(int k) { return (k + 63) / 64 * 64; }
+
+struct TensorDest {
+    int kind = 0;              // 0: bf16 matrix block, 1: fp32 vector (converted)
+    void* dst = nullptr;
+    int rows = 0, cols = 0;    // expected logical shape ([rows] for vectors with cols == 0)
+    int ld = 0;                // destination row stride in elements (matrix)
+    bool scalar = false;       // shape []
+    bool loaded = false;
+};
+
+struct BranchW {
+    gtb_seq_branch d{};
+    std::vector<float> decay;
+    int q_off = 0, k_off = 0, v_off = 0, g_off = 0, a_off = 0;
+    int kq = 0, kk = 0, kv = 0;   // projection widths
+    float* d_pb = nullptr;
+    float* d_decay = nullptr;
+    float* d_inv_freq = nullptr;
+};
+
+struct LayerW {
+    gtb_seq_layer d{};
+    BranchW br[2];
+    int n1 = 0;                // columns of the fused branch projection
+    int kout = 0, kout_p = 0;  // K of the fused out projection
+    int ff = 0;
+    bf16 *w_mix = nullptr, *w_gu = nullptr, *w_out = nullptr, *canon_a = nullptr, *canon_b = nullptr;
+    float* d_gain = nullptr;
+};
+
+struct Run {
+    int layer = 0, pass = -1;  // pass >= 0: inside the loop
+    bool enters_pass = false;  // the loop's entry projection comes before this run
+    void *kc[2] = {nullptr, nullptr}, *vc[2] = {nullptr, nullptr};
+    float* state[2] = {nullptr, nullptr};
+    float* tail = nullptr;
+};
+
+}  // namespace
+
+struct gtb_seq_model {
+    gtb_seq_config cfg{};
+    std::vector<LayerW> L;
+    std::vector<Run> runs;
+    std::map<std::string, TensorDest> tensors;
+    std::vector<void*> allocs;
+    bool finalized = false;
+    int wp = 0;                                  // padded width
+    size_t weight_bytes = 0, state_bytes = 0;
+    bf16 *embed = nullptr, *bigram = nullptr, *head = nullptr, *loop_in = nullptr;
+    float *loop_step = nullptr, *final_gain = nullptr;
+    // workspace of a pass
+    int max_rows = 0, n1_max = 0, ff_max = 0, kout_p_max = 0, ro_max = 0;
+    float *x = nullptr, *x0 = nullptr, *h = nullptr, *P = nullptr, *G = nullptr, *O = nullptr, *logits = nullptr;
+    void *opA = nullptr, *opB = nullptr, *opC = nullptr, *opL = nullptr, *opH = nullptr;
+    float* cap = nullptr;                        // [runs][max_rows][width]
+    bool capture = false;
+    int cap_rows = 0;
+    // tables
+    int* d_tab = nullptr;                        // one upload per pass: seg_slot | seg_row0 | seg_len | row_seg | tok | want
+    int* h_tab = nullptr;                        // pinned
+    int tab_cap = 0;
+    int *d_row_pos = nullptr, *d_row_prev = nullptr, *d_hist = nullptr;
+    SlotState* d_slots = nullptr;
+    std::vector<int> host_pos;
+    std::vector<char> host_stopped_unknown;
+    int last_nseg = 0;                           // rows of `logits` that hold segment-last rows (greedy / decode)
+    bool use_tensor = true;
+    int tensor_min_rows = 64;
+    bool use_graph = true;
+    bool fused_attn = true;
+    SeqGemmPlan* gp = nullptr;
+    // decode graph
+    cudaGraphExec_t graph = nullptr;
+    std::vector<int> graph_slots;
+    int graph_eos = -2;
+};
+
+namespace {
+
+int dalloc(gtb_seq_model* m, void** p, size_t n, bool zero = true) {
+    if (n == 0) n = 16;
+    GTB_CUDA(cudaMalloc(p, n));
+    if (zero) GTB_CUDA(cudaMemsetAsync(*p, 0, n, ctx().stream));
+    m->allocs.push_back(*p);
+    ctx().mem += (int64_t)n;
+    return GTB_OK;
+}
+template <typename T> int dalloc_t(gtb_seq_model* m, T** p, size_t count) { return dalloc(m, reinterpret_cast<void**>(p), count * sizeof(T)); }
+
+void want_matrix(gtb_seq_model* m, const std::string& name, bf16* dst, int rows, int cols, int ld) {
+    TensorDest d; d.kind = 0; d.dst = dst; d.rows = rows; d.cols = cols; d.ld = ld;
+    m->tensors[name] = d;
+    m->weight_bytes += (size_t)rows * cols * 2;
+}
+void want_vector(gtb_seq_model* m, const std::string& name, float* dst, int rows, int cols, bool scalar = false) {
+    TensorDest d; d.kind = 1; d.dst = dst; d.rows = rows; d.cols = cols; d.scalar = scalar;
+    m->tensors[name] = d;
+    m->weight_bytes += (size_t)std::max(rows, 1) * std::max(cols, 1) * 2;
+}
+
+size_t osz(const gtb_seq_model* m) { return m->cfg.mode == GTB_SEQ_F32 ? 4 : 2; }
+
+// C = (acc ? C : 0) + bias + A . W^T on the library stream; picks the tensor-core kernel, the few-row kernel or the SIMT tile kernel
+template <typename OT>
+int product(gtb_seq_model* m, const void* A, int lda, const bf16* W, int ldw, float* C, int ldc, int M, int N, int Kp, const float* bias, int acc) {
+    cudaStream_t st = ctx().stream;
+    const OT* a = reinterpret_cast<const OT*>(A);
+    if (sizeof(OT) == 2 && m->use_tensor && M >= m->tensor_min_rows && m->gp) {
+        int rc = seq_gemm_bf16(m->gp, A, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        if (rc != -1) return rc;                 // -1: shape not supported by that kernel
+    }
+    if (M <= 8) {
+        dim3 grid((N + 7) / 8);
+        if (M <= 2) k_gemv_rows<OT, 2><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        else if (M <= 4) k_gemv_rows<OT, 4><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        else k_gemv_rows<OT, 8><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+    } else {
+        dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
+        k_gemm_simt<OT><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+    }
+    GTB_LAUNCHED();
+    return GTB_OK;
+}
+
+AttnBranch attn_args(const gtb_seq_model* m, const BranchW& b) {
+    AttnBranch a{};
+    a.heads = b.d.heads; a.kv_heads = b.d.kv_heads; a.dim = b.d.dim; a.vdim = b.d.vdim;
+    a.scale = b.d.scale; a.eps = m->cfg.eps; a.out_scale = b.d.out_scale; a.qk_norm = b.d.qk_norm;
+    a.q_off = b.q_off; a.k_off = b.k_off; a.v_off = b.v_off; a.a_off = b.a_off; a.pb = b.d_pb; a.max_ctx = m->cfg.max_ctx;
+    return a;
+}
+RetBranch ret_args(const gtb_seq_model* m, const BranchW& b) {
+    RetBranch a{};
+    a.heads = b.d.heads; a.dim = b.d.dim; a.vdim = b.d.vdim; a.scale = b.d.scale; a.eps = m->cfg.eps; a.out_scale = b.d.out_scale;
+    a.rot_dims = b.d.rot_dims; a.inv_freq = b.d_inv_freq; a.decay = b.d_decay; a.out_norm = b.d.out_norm; a.gated = b.d.gated;
+    a.q_off = b.q_off; a.k_off = b.k_off; a.v_off = b.v_off; a.g_off = b.g_off; a.a_off = b.a_off;
+    return a;
+}
+
+struct RetLaunch { dim3 block; size_t smem; };
+RetLaunch ret_launch(const gtb_seq_branch& d) {
+    RetLaunch r;
+    const int bx = (d.vdim + 31) / 32 * 32;
+    int ny = std::max(1, std::min(std::min(512 / bx, d.dim), 16));
+    r.block = dim3(bx, ny);
+    r.smem = ((size_t)d.dim * d.vdim + 4 * (size_t)d.dim + (size_t)ny * d.vdim) * sizeof(float);
+    return r;
+}
+
+// the launch sequence of one pass: R rows of S segments whose tables are already on the device
+template <typename OT>
+int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pending, int n_want, const int* d_want) {
+    cudaStream_t st = ctx().stream;
+    const gtb_seq_config& c = m->cfg;
+    const int W = c.width, wp = m->wp;
+    OT *opA = (OT*)m->opA, *opB = (OT*)m->opB, *opC = (OT*)m->opC, *opL = (OT*)m->opL, *opH = (OT*)m->opH;
+    k_plan<<<(R + 127) / 128, 128, 0, st>>>(t, R, from_pending ? 1 : 0);
+    GTB_LAUNCHED();
+    k_embed<<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, m->x, c.loop_times > 0 ? m->x0 : nullptr);
+    GTB_LAUNCHED();
+    for (size_t u = 0; u < m->runs.size(); u++) {
+        const Run& run = m->runs[u];
+        const LayerW& l = m->L[run.layer];
+        if (run.enters_pass) {
+            k_concat2<OT><<<R, 256, 0, st>>>(m->x, m->x0, W, opL, pad64(2 * W));
+            GTB_LAUNCHED();
+            int rc = product<OT>(m, opL, pad64(2 * W), m->loop_in, pad64(2 * W), m->x, W, R, W, pad64(2 * W), m->loop_step + (size_t)run.pass * W, 0);
+            if (rc) return rc;
+        }
+        k_rmsnorm_scalar<float><<<R, 256, 0, st>>>(m->x, W, c.eps, l.d_gain, nullptr, m->h, W);
+        GTB_LAUNCHED();
+        OT* ob = l.ff > 0 ? opB : nullptr;
+        if (c.taps > 0) {
+            k_canon<OT><<<R, 256, 0, st>>>(t, m->h, W, c.taps, l.canon_a, l.ff > 0 ? l.canon_b : nullptr, run.tail, opA, ob, wp);
+            GTB_LAUNCHED();
+            if (c.taps > 1) {
+                k_canon_tail<<<S, 256, 0, st>>>(t, m->h, W, c.taps, run.tail);
+                GTB_LAUNCHED();
+            }
+        } else {
+            k_copy_operand<OT><<<R, 256, 0, st>>>(m->h, W, opA, ob, wp);
+            GTB_LAUNCHED();
+        }
+        int rc = product<OT>(m, opA, wp, l.w_mix, wp, m->P, l.n1, R, l.n1, wp, nullptr, 0);
+        if (rc) return rc;
+        if (l.ff > 0) {
+            rc = product<OT>(m, opB, wp, l.w_gu, wp, m->G, 2 * l.ff, R, 2 * l.ff, wp, nullptr, 0);
+            if (rc) return rc;
+        }
+        for (int bi = 0; bi < l.d.n_branches; bi++) {
+            const BranchW& b = l.br[bi];
+            if (b.d.kind == GTB_MIX_SIGMOID_ATTN) {
+                const AttnBranch a = attn_args(m, b);
+                k_attn_prep<OT><<<R, 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[bi], (OT*)run.vc[bi]);
+                GTB_LAUNCHED();
+                k_sigattn<OT><<<dim3(R, a.heads), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], opC, l.kout_p);
+                GTB_LAUNCHED();
+            } else {
+                const RetBranch a = ret_args(m, b);
+                const RetLaunch rl = ret_launch(b.d);
+                if (rl.smem > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_retention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rl.smem));
+                k_retention<<<dim3(S, a.heads), rl.block, rl.smem, st>>>(t, a, m->P, l.n1, run.state[bi], m->O);
+                GTB_LAUNCHED();
+                k_ret_post<OT><<<R, 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
+                GTB_LAUNCHED();
+            }
+        }
+        if (l.ff > 0) {
+            const size_t n = (size_t)R * l.ff;
+            k_geglu<OT><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(m->G, l.ff, opC, l.kout_p, l.kout - l.ff, R);
+            GTB_LAUNCHED();
+        }
+        rc = product<OT>(m, opC, l.kout_p, l.w_out, l.kout_p, m->x, W, R, W, l.kout_p, nullptr, 1);
+        if (rc) return rc;
+        if (m->capture) {
+            GTB_CUDA(cudaMemcpyAsync(m->cap + u * (size_t)m->max_rows * W, m->x, (size_t)R * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
+            m->cap_rows = R;
+        }
+    }
+    if (n_want > 0) {
+        k_rmsnorm_scalar<OT><<<n_want, 256, 0, st>>>(m->x, W, c.eps, m->final_gain, d_want, opH, wp);
+        GTB_LAUNCHED();
+        int rc = product<OT>(m, opH, wp, m->head, wp, m->logits, c.vocab, n_want, c.vocab, wp, nullptr, 0);
+        if (rc) return rc;
+    }
+    k_commit<<<(S + 127) / 128, 128, 0, st>>>(t, S);
+    GTB_LAUNCHED();
+    return GTB_OK;
+}
+
+}  // namespace
+
+// the table buffer of a pass: ints [seg_slot S | seg_row0 S | seg_len S | row_seg R | tok R | want R]
+static PassTables tables(gtb_seq_model* m, int S, int R) {
+    PassTables t{};
+    int* b = m->d_tab;
+    t.seg_slot = b; t.seg_row0 = b + S; t.seg_len = b + 2 * S; t.row_seg = b + 3 * S; t.tok = b + 3 * S + R;
+    t.row_pos = m->d_row_pos; t.row_prev = m->d_row_prev; t.slots = m->d_slots;
+    return t;
+}
+
+extern "C" {
+
+int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_layer* layers) {
+    GTB_CHECK_INIT();
+    GTB_ARG(out && cfg && layers);
+    GTB_ARG(cfg->vocab > 0 && cfg->width > 0 && cfg->n_layers > 0 && cfg->n_slots > 0 && cfg->max_ctx > 0);
+    GTB_ARG(cfg->mode == GTB_SEQ_BF16 || cfg->mode == GTB_SEQ_F32);
+    GTB_ARG(cfg->taps >= 0 && cfg->taps <= 64);
+    if (cfg->loop_times > 0) GTB_ARG(cfg->loop_start >= 0 && cfg->loop_start < cfg->loop_stop && cfg->loop_stop <= cfg->n_layers);
+    gtb_seq_model* m = new gtb_seq_model();
+    m->cfg = *cfg;
+    gtb_seq_config& c = m->cfg;
+    if (c.max_rows <= 0) c.max_rows = 2048;
+    m->max_rows = c.max_rows;
+    const int W = c.width, wp = pad64(W);
+    m->wp = wp;
+    int rc = GTB_OK;
+#define TRY(e) do { rc = (e); if (rc) { gtb_seq_destroy(m); return rc; } } while (0)
+#define REQ(cond) do { if (!(cond)) { gtb_seq_destroy(m); return gtb::fail(GTB_ERR_ARG, "model description rejected: %s", #cond); } } while (0)
+    TRY(dalloc_t(m, &m->embed, (size_t)c.vocab * W));
+    want_matrix(m, "embed", m->embed, c.vocab, W, W);
+    if (c.bigram_buckets > 0) {
+        TRY(dalloc_t(m, &m->bigram, (size_t)(c.bigram_buckets + 1) * W));
+        want_matrix(m, "bigram", m->bigram, c.bigram_buckets + 1, W, W);
+    }
+    TRY(dalloc_t(m, &m->head, (size_t)c.vocab * wp));
+    want_matrix(m, "head", m->head, c.vocab, W, wp);
+    TRY(dalloc_t(m, &m->final_gain, 1));
+    want_vector(m, "final.norm", m->final_gain, 0, 0, true);
+    if (c.loop_times > 0) {
+        TRY(dalloc_t(m, &m->loop_in, (size_t)W * pad64(2 * W)));
+        want_matrix(m, "loop.in", m->loop_in, W, 2 * W, pad64(2 * W));
+        TRY(dalloc_t(m, &m->loop_step, (size_t)c.loop_times * W));
+        want_vector(m, "loop.step", m->loop_step, c.loop_times, W);
+    }
+    m->L.resize(c.n_layers);
+    for (int i = 0; i < c.n_layers; i++) {
+        LayerW& l = m->L[i];
+        l.d = layers[i];
+        REQ(l.d.n_branches >= 1 && l.d.n_branches <= 2);
+        REQ(l.d.ff >= 0);
+        l.ff = l.d.ff;
+        const std::string lp = "l" + std::to_string(i) + ".";
+        int n1 = 0, ko = 0;
+        for (int bi = 0; bi < l.d.n_branches; bi++) {
+            BranchW& b = l.br[bi];
+            b.d = l.d.branch[bi];
+            gtb_seq_branch& d = b.d;
+            REQ(d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_RETENTION);
+            REQ(d.heads > 0 && d.dim > 0 && d.vdim > 0 && d.dim <= 1024 && d.vdim <= 512);
+            if (d.kind == GTB_MIX_RETENTION) d.kv_heads = d.heads;
+            REQ(d.kv_heads > 0 && d.heads % d.kv_heads == 0);
+            REQ(d.rot_dims >= 0 && d.rot_dims <= d.dim && d.rot_dims % 2 == 0);
+            b.kq = d.heads * d.dim; b.kk = d.kv_heads * d.dim; b.kv = d.kv_heads * d.vdim;
+            b.q_off = n1; b.k_off = n1 + b.kq; b.v_off = b.k_off + b.kk; n1 = b.v_off + b.kv;
+            if (d.kind == GTB_MIX_RETENTION && d.gated) { b.g_off = n1; n1 += d.heads * d.vdim; }
+            b.a_off = ko; ko += d.heads * d.vdim;
+            if (d.kind == GTB_MIX_RETENTION) {
+                REQ(d.decay != nullptr);
+                REQ(ret_launch(d).smem <= 200 * 1024);
+                b.decay.assign(d.decay, d.decay + d.heads);
+                d.decay = nullptr;
+                TRY(dalloc_t(m, &b.d_decay, d.heads));
+                GTB_CUDA(cudaMemcpyAsync(b.d_decay, b.decay.data(), d.heads * sizeof(float), cudaMemcpyHostToDevice, ctx().stream));
+                if (d.rot_dims > 0) {
+                    std::vector<float> f(d.rot_dims / 2);
+                    for (int k = 0; k < d.rot_dims / 2; k++) f[k] = (float)pow((double)d.rot_base, -2.0 * k / d.rot_dims);
+                    TRY(dalloc_t(m, &b.d_inv_freq, f.size()));
+                    GTB_CUDA(cudaMemcpy(b.d_inv_freq, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
+                }
+            }
+        }
+        GTB_CUDA(cudaStreamSynchronize(ctx().stream));       // the decay vectors above are read from temporaries of this loop
+        l.n1 = n1;
+        l.kout = ko + l.ff;
+        l.kout_p = pad64(l.kout);
+        TRY(dalloc_t(m, &l.w_mix, (size_t)n1 * wp));
+        TRY(dalloc_t(m, &l.w_out, (size_t)W * l.kout_p));
+        for (int bi = 0; bi < l.d.n_branches; bi++) {
+            BranchW& b = l.br[bi];
+            const std::string bp = lp + "mix." + (b.d.name[0] ? std::string(b.d.name) + "." : std::string());
+            want_matrix(m, bp + "q", l.w_mix + (size_t)b.q_off * wp, b.kq, W, wp);
+            want_matrix(m, bp + "k", l.w_mix + (size_t)b.k_off * wp, b.kk, W, wp);
+            want_matrix(m, bp + "v", l.w_mix + (size_t)b.v_off * wp, b.kv, W, wp);
+            if (b.d.kind == GTB_MIX_RETENTION && b.d.gated) want_matrix(m, bp + "g", l.w_mix + (size_t)b.g_off * wp, b.d.heads * b.d.vdim, W, wp);
+            want_matrix(m, bp + "o", l.w_out + b.a_off, W, b.d.heads * b.d.vdim, l.kout_p);
+            if (b.d.kind == GTB_MIX_SIGMOID_ATTN) {
+                TRY(dalloc_t(m, &b.d_pb, b.d.heads));
+                want_vector(m, bp + "pb", b.d_pb, b.d.heads, 0);
+            }
+        }
+        if (l.ff > 0) {
+            TRY(dalloc_t(m, &l.w_gu, (size_t)2 * l.ff * wp));
+            want_matrix(m, lp + "mlp.gate", l.w_gu, l.ff, W, wp);
+            want_matrix(m, lp + "mlp.up", l.w_gu + (size_t)l.ff * wp, l.ff, W, wp);
+            want_matrix(m, lp + "mlp.down", l.w_out + ko, W, l.ff, l.kout_p);
+        }
+        TRY(dalloc_t(m, &l.d_gain, 1));
+        want_vector(m, lp + "norm1", l.d_gain, 0, 0, true);
+        if (c.taps > 0) {
+            TRY(dalloc_t(m, &l.canon_a, (size_t)W * c.taps));
+            want_matrix(m, lp + "canon1", l.canon_a, W, c.taps, c.taps);
+            if (l.ff > 0) {
+                TRY(dalloc_t(m, &l.canon_b, (size_t)W * c.taps));
+                want_matrix(m, lp + "canon2", l.canon_b, W, c.taps, c.taps);
+            }
+        }
+        m->n1_max = std::max(m->n1_max, n1);
+        m->ff_max = std::max(m->ff_max, l.ff);
+        m->kout_p_max = std::max(m->kout_p_max, l.kout_p);
+        for (int bi = 0; bi < l.d.n_branches; bi++)
+            if (l.br[bi].d.kind == GTB_MIX_RETENTION) m->ro_max = std::max(m->ro_max, l.br[bi].d.heads * l.br[bi].d.vdim);
+    }
+    // the order of layer runs
+    auto add_run = [&](int layer, int pass, bool enters) { Run r; r.layer = layer; r.pass = pass; r.enters_pass = enters; m->runs.push_back(r); };
+    if (c.loop_times > 0) {
+        for (int i = 0; i < c.loop_start; i++) add_run(i, -1, false);
+        for (int p = 0; p < c.loop_times; p++)
+            for (int i = c.loop_start; i < c.loop_stop; i++) add_run(i, p, i == c.loop_start);
+        for (int i = c.loop_stop; i < c.n_layers; i++) add_run(i, -1, false);
+    } else {
+        for (int i = 0; i < c.n_layers; i++) add_run(i, -1, false);
+    }
+    // state of every run, for every slot
+    const size_t es = osz(m);
+    for (Run& r : m->runs) {
+        const LayerW& l = m->L[r.layer];
+        size_t per_slot = 0;
+        for (int bi = 0; bi < l.d.n_branches; bi++) {
+            const gtb_seq_branch& d = l.br[bi].d;
+            if (d.kind == GTB_MIX_SIGMOID_ATTN) {
+                const size_t kb = (size_t)c.max_ctx * d.kv_heads * d.dim * es, vb = (size_t)c.max_ctx * d.kv_heads * d.vdim * es;
+                TRY(dalloc(m, &r.kc[bi], kb * c.n_slots));
+                TRY(dalloc(m, &r.vc[bi], vb * c.n_slots));
+                per_slot += kb + vb;
+            } else {
+                const size_t sb = (size_t)d.heads * d.dim * d.vdim * sizeof(float);
+                TRY(dalloc(m, (void**)&r.state[bi], sb * c.n_slots));
+                per_slot += sb;
+            }
+        }
+        if (c.taps > 1) {
+            TRY(dalloc_t(m, &r.tail, (size_t)c.n_slots * (c.taps - 1) * W));
+            per_slot += (size_t)(c.taps - 1) * W * sizeof(float);
+        }
+        m->state_bytes += per_slot;
+    }
+    // workspace
+    const size_t R = m->max_rows;
+    TRY(dalloc_t(m, &m->x, R * W));
+    TRY(dalloc_t(m, &m->x0, R * W));
+    TRY(dalloc_t(m, &m->h, R * W));
+    TRY(dalloc_t(m, &m->P, R * m->n1_max));
+    TRY(dalloc_t(m, &m->G, R * 2 * std::max(m->ff_max, 1)));
+    TRY(dalloc_t(m, &m->O, R * std::max(m->ro_max, 1)));
+    TRY(dalloc_t(m, &m->logits, R * c.vocab));
+    TRY(dalloc(m, &m->opA, R * wp * es));
+    TRY(dalloc(m, &m->opB, R * wp * es));
+    TRY(dalloc(m, &m->opC, R * m->kout_p_max * es));
+    TRY(dalloc(m, &m->opL, R * pad64(2 * W) * es));
+    TRY(dalloc(m, &m->opH, R * wp * es));
+    m->tab_cap = 3 * c.n_slots + 3 * (int)R + 16;
+    TRY(dalloc_t(m, &m->d_tab, m->tab_cap));
+    GTB_CUDA(cudaHostAlloc((void**)&m->h_tab, m->tab_cap * sizeof(int), cudaHostAllocDefault));
+    TRY(dalloc_t(m, &m->d_row_pos, R));
+    TRY(dalloc_t(m, &m->d_row_prev, R));
+    TRY(dalloc_t(m, &m->d_hist, (size_t)c.n_slots * 2));
+    TRY(dalloc_t(m, &m->d_slots, c.n_slots));
+    m->host_pos.assign(c.n_slots, 0);
+    for (int s = 0; s < c.n_slots; s++) TRY(gtb_seq_slot_reset(m, s));
+    if (c.mode == GTB_SEQ_BF16) seq_gemm_create(&m->gp);     // a failure leaves gp null: SIMT kernels only
+#undef TRY
+#undef REQ
+    GTB_CUDA(cudaStreamSynchronize(ctx().stream));
+    *out = m;
+    return GTB_OK;
+}
+
+int gtb_seq_destroy(gtb_seq_t m) {
+    if (!m) return GTB_OK;
+    cudaStreamSynchronize(ctx().stream);
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    if (m->gp) seq_gemm_destroy(m->gp);
+    for (void* p : m->allocs) cudaFree(p);
+    if (m->h_tab) cudaFreeHost(m->h_tab);
+    delete m;
+    return GTB_OK;
+}
+
+int gtb_seq_set_tensor(gtb_seq_t m, const char* name, const void* h_bf16, const int64_t* shape, int ndim) {
+    GTB_CHECK_INIT();
+    GTB_ARG(m && name && h_bf16 && ndim >= 0 && ndim <= 2);
+    auto it = m->tensors.find(name);
+    if (it == m->tensors.end()) return gtb::fail(GTB_ERR_ARG, "tensor '%s' does not belong to this model", name);
+    TensorDest& d = it->second;
+    const int64_t r = ndim >= 1 ? shape[0] : 0, cc = ndim >= 2 ? shape[1] : 0;
+    bool ok;
+    if (d.scalar) ok = ndim == 0 || (ndim == 1 && r == 1);
+    else if (d.kind == 1 && d.cols == 0) ok = ndim == 1 && r == d.rows;
+    else ok = ndim == 2 && r == d.rows && cc == d.cols;
+    if (!ok) return gtb::fail(GTB_ERR_ARG, "tensor '%s': shape does not fit the description (expected [%d, %d])", name, d.rows, d.cols);
+    if (d.kind == 0) {
+        GTB_CUDA(cudaMemcpy2D(d.dst, (size_t)d.ld * 2, h_bf16, (size_t)d.cols * 2, (size_t)d.cols * 2, d.rows, cudaMemcpyHostToDevice));
+    } else {
+        const size_t n = d.scalar ? 1 : (size_t)d.rows * std::max(d.cols, 1);
+        std::vector<float> f(n);
+        const uint16_t* s = reinterpret_cast<const uint16_t*>(h_bf16);
+        for (size_t i = 0; i < n; i++) { const uint32_t u = (uint32_t)s[i] << 16; memcpy(&f[i], &u, 4); }
+        GTB_CUDA(cudaMemcpy(d.dst, f.data(), n * sizeof(float), cudaMemcpyHostToDevice));
+    }
+    d.loaded = true;
+    return GTB_OK;
+}
+
+int gtb_seq_finalize(gtb_seq_t m) {
+    GTB_ARG(m);
+    for (auto& kv : m->tensors)
+        if (!kv.second.loaded) return gtb::fail(GTB_ERR_STATE, "tensor '%s' has not been loaded", kv.first.c_str());
+    m->finalized = true;
+    return GTB_OK;
+}
+
+int gtb_seq_n_runs(gtb_seq_t m, int* n) { GTB_ARG(m && n); *n = (int)m->runs.size(); return GTB_OK; }
+
+int gtb_seq_slot_reset(gtb_seq_t m, int slot) {
+    GTB_CHECK_INIT();
+    GTB_ARG(m && slot >= 0 && slot < m->cfg.n_slots);
+    cudaStream_t st = ctx().stream;
+    const SlotState z{0, -1, 0, 0};
+    GTB_CUDA(cudaMemcpyAsync(m->d_slots + slot, &z, sizeof z, cudaMemcpyHostToDevice, st));
+    GTB_CUDA(cudaStreamSynchronize(st));                    // z is a local
+    for (Run& r : m->runs) {
+        const LayerW& l = m->L[r.layer];
+        for (int bi = 0; bi < l.d.n_branches; bi++)
+            if (r.state[bi]) {
+                const size_t sb = (size_t)l.br[bi].d.heads * l.br[bi].d.dim * l.br[bi].d.vdim * sizeof(float);
+                GTB_CUDA(cudaMemsetAsync((char*)r.state[bi] + sb * slot, 0, sb, st));
+            }
+        if (r.tail) {
+            const size_t tb = (size_t)(m->cfg.taps - 1) * m->cfg.width * sizeof(float);
+            GTB_CUDA(cudaMemsetAsync((char*)r.tail + tb * slot, 0, tb, st));
+        }
+    }
+    m->host_pos[slot] = 0;
+    return GTB_OK;
+}
+
+int gtb_seq_slot_position(gtb_seq_t m, int slot, int* pos) {
+    GTB_CHECK_INIT();
+    GTB_ARG(m && pos && slot >= 0 && slot < m->cfg.n_slots);
+    SlotState s;
+    GTB_CUDA(cudaMemcpyAsync(&s, m->d_slots + slot, sizeof s, cudaMemcpyDeviceToHost, ctx().stream));
+    GTB_CUDA(cudaStreamSynchronize(ctx().stream));
+    *pos = s.pos;
+    m->host_pos[slot] = s.pos;
+    return GTB_OK;
+}
+
+static int step_impl(gtb_seq_t m, int n_seg, const int32_t* seg_slot, const int32_t* seg_len, const int32_t* h_tokens, int n_want,
+                     const int32_t* want_rows, float* h_logits, bool greedy, int32_t* h_next) {
+    GTB_CHECK_INIT();
+    GTB_ARG(m && n_seg > 0 && n_seg <= m->cfg.n_slots && seg_slot && seg_len && h_tokens);
+    if (!m->finalized) return gtb::fail(GTB_ERR_STATE, "gtb_seq_finalize has not succeeded");
+    cudaStream_t st = ctx().stream;
+    const gtb_seq_config& c = m->cfg;
+    std::vector<char> seen(c.n_slots, 0);
+    long long total = 0;
+    for (int s = 0; s < n_seg; s++) {
+        GTB_ARG(seg_slot[s] >= 0 && seg_slot[s] < c.n_slots && !seen[seg_slot[s]] && seg_len[s] > 0);
+        seen[seg_slot[s]] = 1;
+        if (m->host_pos[seg_slot[s]] + seg_len[s] > c.max_ctx)
+            return gtb::fail(GTB_ERR_ARG, "slot %d: %d + %d tokens exceed max_ctx %d", seg_slot[s], m->host_pos[seg_slot[s]], seg_len[s], c.max_ctx);
+        total += seg_len[s];
+    }
+    for (long long i = 0; i < total; i++) GTB_ARG(h_tokens[i] >= 0 && h_tokens[i] < c.vocab);
+    if (greedy) { GTB_ARG(h_next); n_want = 0; }
+    for (int i = 0; i < n_want; i++) GTB_ARG(want_rows[i] >= 0 && want_rows[i] < total && (i == 0 || want_rows[i] > want_rows[i - 1]));
+    if (n_want > 0) GTB_ARG(h_logits);
+    // passes: walk the segments, cutting at max_rows rows
+    int seg = 0, off = 0, wi = 0, row_base = 0;
+    std::vector<int> next(n_seg, 0);
+    while (seg < n_seg) {
+        int* tb = m->h_tab;
+        std::vector<int> ps, pr0, pl, pseg_of;      // this pass's segments
+        int R = 0;
+        int s = seg, o = off;
+        while (s < n_seg && R < m->max_rows) {
+            const int take = std::min(seg_len[s] - o, m->max_rows - R);
+            ps.push_back(seg_slot[s]); pr0.push_back(R); pl.push_back(take); pseg_of.push_back(s);
+            R += take; o += take;
+            if (o == seg_len[s]) { s++; o = 0; }
+        }
+        const int S = (int)ps.size();
+        std::vector<int> want_local, last_rows;
+        while (wi < n_want && want_rows[wi] < row_base + R) want_local.push_back(want_rows[wi++] - row_base);
+        std::vector<int> greedy_segs;
+        if (greedy)
+            for (int k = 0; k < S; k++) {
+                const int gs = pseg_of[k];
+                const bool ends = (gs < s) || (gs == s && o == 0);       // the segment's last row is inside this pass
+                if (ends) { want_local.push_back(pr0[k] + pl[k] - 1); greedy_segs.push_back(k); }
+            }
+        int* p = tb;
+        memcpy(p, ps.data(), S * 4); p += S;
+        memcpy(p, pr0.data(), S * 4); p += S;
+        memcpy(p, pl.data(), S * 4); p += S;
+        for (int k = 0; k < S; k++) for (int i = 0; i < pl[k]; i++) *p++ = k;
+        memcpy(p, h_tokens + row_base, R * 4); p += R;
+        const int nw = (int)want_local.size();
+        if (nw) memcpy(p, want_local.data(), nw * 4);
+        const int n_ints = 3 * S + 2 * R + nw;
+        GTB_CUDA(cudaMemcpyAsync(m->d_tab, tb, n_ints * sizeof(int), cudaMemcpyHostToDevice, st));
+        const PassTables t = tables(m, S, R);
+        const int* d_want = m->d_tab + 3 * S + 2 * R;
+        int rc;
+        // greedy passes: logits rows are ordered like greedy_segs; the argmax kernel needs a segment per logits row, so it runs on
+        // a table of its own below
+        if (c.mode == GTB_SEQ_F32) rc = run_pass<float>(m, t, R, S, false, nw, d_want);
+        else rc = run_pass<bf16>(m, t, R, S, false, nw, d_want);
+        if (rc) return rc;
+        if (greedy && nw) {
+            // segment table restricted to the segments that ended: reuse the upload buffer behind the pass's tables
+            int* q = m->h_tab + n_ints;
+            for (int k : greedy_segs) *q++ = ps[k];
+            GTB_CUDA(cudaMemcpyAsync(m->d_tab + n_ints, m->h_tab + n_ints, nw * sizeof(int), cudaMemcpyHostToDevice, st));
+            PassTables ta = t;
+            ta.seg_slot = m->d_tab + n_ints;
+            k_argmax_rows<<<nw, 1024, 0, st>>>(m->logits, c.vocab, ta, -1, m->d_hist, 1, 0);
+            GTB_LAUNCHED();
+            std::vector<int> got(nw);
+            GTB_CUDA(cudaMemcpyAsync(got.data(), m->d_hist, nw * sizeof(int), cudaMemcpyDeviceToHost, st));
+            GTB_CUDA(cudaStreamSynchronize(st));
+            for (int i = 0; i < nw; i++) h_next[pseg_of[greedy_segs[i]]] = got[i];
+            m->last_nseg = nw;
+        } else if (nw) {
+            GTB_CUDA(cudaMemcpyAsync(h_logits + (size_t)(wi - nw) * c.vocab, m->logits, (size_t)nw * c.vocab * sizeof(float), cudaMemcpyDeviceToHost, st));
+            GTB_CUDA(cudaStreamSynchronize(st));
+        } else {
+            GTB_CUDA(cudaStreamSynchronize(st));       // the pinned table buffer is reused by the next pass
+        }
+        for (int k = 0; k < S; k++) m->host_pos[ps[k]] += pl[k];
+        row_base += R;
+        seg = s; off = o;
+    }
+    (void)next;
+    return GTB_OK;
+}
+
+int gtb_seq_step(gtb_seq_t m, int n_seg, const int32_t* seg_slot, const int32_t* seg_len, const int32_t* h_tokens, int n_want,
+                 const int32_t* want_rows, float* h_logits) {
+    return step_impl(m, n_seg, seg_slot, seg_len, h_tokens, n_want, want_rows, h_logits, false, nullptr);
+}
+
+int gtb_seq_step_greedy(gtb_seq_t m, int n_seg, const int32_t* seg_slot, const int32_t* seg_len, const int32_t* h_tokens, int32_t* h_next) {
+    return step_impl(m, n_seg, seg_slot, seg_len, h_tokens, 0, nullptr, nullptr, true, h_next);
+}
+
+int gtb_seq_decode(gtb_seq_t m, int n, const int32_t* slots, int n_steps, int eos_id, int32_t* h_out) {
+    GTB_CHECK_INIT();
+    GTB_ARG(m && n > 0 && n <= m->cfg.n_slots && n <= m->max_rows && slots && n_steps > 0 && h_out);
+    if (!m->finalized) return gtb::fail(GTB_ERR_STATE, "gtb_seq_finalize has not succeeded");
+    cudaStream_t st = ctx().stream;
+    const gtb_seq_config& c = m->cfg;
+    std::vector<char> seen(c.n_slots, 0);
+    for (int i = 0; i < n; i++) {
+        GTB_ARG(slots[i] >= 0 && slots[i] < c.n_slots && !seen[slots[i]]);
+        seen[slots[i]] = 1;
+        if (m->host_pos[slots[i]] + n_steps > c.max_ctx)
+            return gtb::fail(GTB_ERR_ARG, "slot %d: %d + %d tokens exceed max_ctx %d", slots[i], m->host_pos[slots[i]], n_steps, c.max_ctx);
+    }
+    const bool same = m->graph && m->graph_eos == eos_id && m->graph_slots.size() == (size_t)n && std::equal(slots, slots + n, m->graph_slots.begin());
+    // tables of a decode pass: segment i = slot i, one row each, wanted rows = all
+    int* p = m->h_tab;
+    for (int i = 0; i < n; i++) *p++ = slots[i];
+    for (int i = 0; i < n; i++) *p++ = i;
+    for (int i = 0; i < n; i++) *p++ = 1;
+    for (int i = 0; i < n; i++) *p++ = i;      // row_seg
+    for (int i = 0; i < n; i++) *p++ = 0;      // tok (from pending)
+    for (int i = 0; i < n; i++) *p++ = i;      // want
+    GTB_CUDA(cudaMemcpyAsync(m->d_tab, m->h_tab, 6 * n * sizeof(int), cudaMemcpyHostToDevice, st));
+    const PassTables t = tables(m, n, n);
+    const int* d_want = m->d_tab + 5 * n;
+    int* d_out = nullptr;
+    GTB_CUDA(cudaMalloc((void**)&d_out, (size_t)n * n_steps * sizeof(int)));
+    auto one = [&]() -> int {
+        int rc = c.mode == GTB_SEQ_F32 ? run_pass<float>(m, t, n, n, true, n, d_want) : run_pass<bf16>(m, t, n, n, true, n, d_want);
+        if (rc) return rc;
+        k_argmax_rows<<<n, 1024, 0, st>>>(m->logits, c.vocab, t, eos_id, m->d_hist, 1, 0);
+        GTB_LAUNCHED();
+        return GTB_OK;
+    };
+    int rc = GTB_OK;
+    if (m->use_graph && !m->capture) {
+        if (!same) {
+            if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+            const int64_t l0 = ctx().launches;
+            cudaGraph_t g = nullptr;
+            GTB_CUDA(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+            rc = one();
+            cudaError_t ce = cudaStreamEndCapture(st, &g);
+            ctx().launches = l0;
+            if (rc) { if (g) cudaGraphDestroy(g); cudaFree(d_out); return rc; }
+            if (ce != cudaSuccess) { cudaFree(d_out); return gtb::fail(GTB_ERR_CUDA, "graph capture failed: %s", cudaGetErrorString(ce)); }
+            ce = cudaGraphInstantiate(&m->graph, g, 0);
+            cudaGraphDestroy(g);
+            if (ce != cudaSuccess) { cudaFree(d_out); return gtb::fail(GTB_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(ce)); }
+            m->graph_slots.assign(slots, slots + n);
+            m->graph_eos = eos_id;
+        }
+    }
+    for (int k = 0; k < n_steps && rc == GTB_OK; k++) {
+        if (m->use_graph && !m->capture) {
+            cudaError_t ce = cudaGraphLaunch(m->graph, st);
+            if (ce != cudaSuccess) rc = gtb::fail(GTB_ERR_CUDA, "graph launch failed: %s", cudaGetErrorString(ce));
+            ctx().launches += 1;
+        } else {
+            rc = one();
+        }
+        if (rc == GTB_OK) {
+            cudaError_t ce = cudaMemcpy2DAsync(d_out + k, (size_t)n_steps * sizeof(int), m->d_hist, sizeof(int), sizeof(int), n, cudaMemcpyDeviceToDevice, st);
+            if (ce != cudaSuccess) rc = gtb::fail(GTB_ERR_CUDA, "copy failed: %s", cudaGetErrorString(ce));
+        }
+    }
+    if (rc == GTB_OK) {
+        cudaError_t ce = cudaMemcpyAsync(h_out, d_out, (size_t)n * n_steps * sizeof(int), cudaMemcpyDeviceToHost, st);
+        if (ce == cudaSuccess) ce = cudaStreamSynchronize(st);
+        if (ce != cudaSuccess) rc = gtb::fail(GTB_ERR_CUDA, "copy failed: %s", cudaGetErrorString(ce));
+    }
+    cudaFree(d_out);
+    if (rc) return rc;
+    m->last_nseg = n;
+    for (int i = 0; i < n; i++) { int pos; gtb_seq_slot_position(m, slots[i], &pos); }
+    return GTB_OK;
+}
+
+int gtb_seq_topk(gtb_seq_t m, int seg, int k, float* h_values, int32_t* h_ids) {
+    GTB_CHECK_INIT();
+    GTB_ARG(m && seg >= 0 && seg < m->last_nseg && k > 0 && k <= 64 && k <= m->cfg.vocab && h_values && h_ids);
+    float* dv = nullptr;
+    GTB_CUDA(cudaMalloc((void**)&dv, 64 * (sizeof(float) + sizeof(int32_t))));
+    int32_t* di = reinterpret_cast<int32_t*>(dv + 64);
+    k_topk<<<1, 1024, 0, ctx().stream>>>(m->logits + (size_t)seg * m->cfg.vocab, m->cfg.vocab, k, dv, di);
+    ctx().launches++;
+    cudaError_t e = cudaMemcpyAsync(h_values, dv, k * sizeof(float), cudaMemcpyDeviceToHost, ctx().stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_ids, di, k * sizeof(int32_t), cudaMemcpyDeviceToHost, ctx().stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(ctx().stream);
+    cudaFree(dv);
+    if (e != cudaSuccess) return gtb::fail(GTB_ERR_CUDA, "top-k failed: %s", cudaGetErrorString(e));
+    return GTB_OK;
+}
+
+int gtb_seq_last_logits(gtb_seq_t m, int seg, float* h_logits) {
+    GTB_CHECK_INIT();
+    GTB_ARG(m && seg >= 0 && seg < m->last_nseg && h_logits);
+    GTB_CUDA(cudaMemcpyAsync(h_logits, m->logits + (size_t)seg * m->cfg.vocab, m->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, ctx().stream));
+    GTB_CUDA(cudaStreamSynchronize(ctx().stream));
+    return GTB_OK;
+}
+
+int gtb_seq_set_option(gtb_seq_t m, const char* name, int value) {
+    GTB_ARG(m && name);
+    const std::string n = name;
+    if (n == "capture") {
+        m->capture = value != 0;
+        if (m->capture && !m->cap) {
+            int rc = dalloc_t(m, &m->cap, m->runs.size() * (size_t)m->max_rows * m->cfg.width);
+            if (rc) return rc;
+        }
+    } else if (n == "tensor") m->use_tensor = value != 0;
+    else if (n == "tensor_min_rows") m->tensor_min_rows = std::max(1, value);
+    else if (n == "graph") m->use_graph = value != 0;
+    else if (n == "fused_attn") m->fused_attn = value != 0;
+    else return gtb::fail(GTB_ERR_ARG, "unknown option '%s'", name);
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    return GTB_OK;
+}
+
+int gtb_seq_read_capture(gtb_seq_t m, int run, int row, float* h_out) {
+    GTB_CHECK_INIT();
+    GTB_ARG(m && m->cap && run >= 0 && run < (int)m->runs.size() && row >= 0 && row < m->cap_rows && h_out);
+    GTB_CUDA(cudaMemcpyAsync(h_out, m->cap + ((size_t)run * m->max_rows + row) * m->cfg.width, m->cfg.width * sizeof(float), cudaMemcpyDeviceToHost, ctx().stream));
+    GTB_CUDA(cudaStreamSynchronize(ctx().stream));
+    return GTB_OK;
+}
+
+int gtb_seq_weight_bytes(gtb_seq_t m, size_t* nbytes) { GTB_ARG(m && nbytes); *nbytes = m->weight_bytes; return GTB_OK; }
+int gtb_seq_state_bytes_per_slot(gtb_seq_t m, size_t* nbytes) { GTB_ARG(m && nbytes); *nbytes = m->state_bytes; return GTB_OK; }
+
+}  // extern "C"

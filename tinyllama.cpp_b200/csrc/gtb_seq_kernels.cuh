@@ -1,0 +1,500 @@
+// gtb_seq_kernels.cuh -- device side of the layer-list sequence models (include/gten_b200_seq.h).
+//
+// One pass = R rows (tokens) of S segments; segment s continues slot seg_slot[s] for seg_len[s] rows starting at row seg_row0[s].
+// Everything the kernels need to know about a row sits in the device-side PassTables, so a pass is a fixed launch
+// sequence whatever the positions are (CUDA-graph replay for decode steps).
+//
+// Precision: the residual stream, norms, convolution, attention scores and weights, the recurrent state and everything that
+// enters the recurrence are fp32 in both compute modes.  OT is the type of matrix-product operands and of the K/V cache:
+// __nv_bfloat16 (products on bf16 operands with fp32 accumulation) or float (true fp32, FFMA only).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace gtb {
+namespace seq {
+
+typedef __nv_bfloat16 bf16;
+
+struct SlotState {
+    int pos;          // tokens held
+    int prev;         // last token fed (-1: none)
+    int pending;      // last sampled token: what the next device-driven decode step feeds
+    int stopped;      // sampled the end-of-sequence id
+};
+
+struct PassTables {
+    // per segment
+    const int* seg_slot;
+    const int* seg_row0;
+    const int* seg_len;
+    // per row
+    const int* row_seg;
+    int* tok;          // token ids (host-fed, or written by k_plan from SlotState::pending)
+    int* row_pos;      // written by k_plan
+    int* row_prev;     // previous token of the row, -1 for a sequence's first token; written by k_plan
+    SlotState* slots;
+};
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<bf16>(const bf16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ T cvt(float v);
+template <> __device__ __forceinline__ float cvt<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 cvt<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+// sum over the block; every thread gets the result.  red: 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();                 // red may still be read from a previous call
+    if (lane == 0) red[wid] = v;
+    __syncthreads();
+    if (wid == 0) {
+        float t = lane < nw ? red[lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float gelu_tanh(float z) {
+    const float c = 0.7978845608028654f;      // sqrt(2/pi)
+    return 0.5f * z * (1.0f + tanhf(c * (z + 0.044715f * z * z * z)));
+}
+
+// ------------------------------------------------------------------------------------------------ plan / commit
+// row tables of a pass from the slots' device-side state.  from_pending: rows take their token from the slot (decode loop).
+__global__ void k_plan(PassTables t, int R, int from_pending) {
+    const int r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= R) return;
+    const int s = t.row_seg[r], slot = t.seg_slot[s], row0 = t.seg_row0[s];
+    const SlotState st = t.slots[slot];
+    if (from_pending) t.tok[r] = st.pending;
+    const int pos = st.pos + (r - row0);
+    t.row_pos[r] = pos;
+    t.row_prev[r] = (r > row0) ? (from_pending ? st.pending : t.tok[r - 1]) : (pos == 0 ? -1 : st.prev);
+}
+__global__ void k_commit(PassTables t, int S) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= S) return;
+    SlotState& st = t.slots[t.seg_slot[s]];
+    if (st.stopped) return;
+    st.pos += t.seg_len[s];
+    st.prev = t.tok[t.seg_row0[s] + t.seg_len[s] - 1];
+}
+
+// ------------------------------------------------------------------------------------------------ embedding
+// x = embed[tok] (+ bigram[(prev * mul_prev + tok * mul_cur) mod buckets], row `buckets` for a sequence's first token); x0 = x
+__global__ void k_embed(PassTables t, const bf16* __restrict__ embed, const bf16* __restrict__ bigram, int buckets, int mul_prev,
+                        int mul_cur, int width, float* __restrict__ x, float* __restrict__ x0) {
+    const int r = blockIdx.x;
+    const int tok = t.tok[r], prev = t.row_prev[r];
+    long long row = buckets;
+    if (prev >= 0) row = ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = __bfloat162float(embed[(size_t)tok * width + c]);
+        if (buckets > 0) v += __bfloat162float(bigram[(size_t)row * width + c]);
+        x[(size_t)r * width + c] = v;
+        if (x0) x0[(size_t)r * width + c] = v;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ norm with one gain
+// h = x / sqrt(mean(x^2) + eps) * g, g a single number.  rows: optional gather (row index per output row).
+template <typename OUT>
+__global__ void k_rmsnorm_scalar(const float* __restrict__ x, int width, float eps, const float* __restrict__ g, const int* __restrict__ rows,
+                                 OUT* __restrict__ out, int ld_out) {
+    __shared__ float red[33];
+    const int o = blockIdx.x, r = rows ? rows[o] : o;
+    const float* xr = x + (size_t)r * width;
+    float ss = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = xr[c]; ss += v * v; }
+    ss = block_sum(ss, red);
+    const float sc = (1.0f / sqrtf(ss / (float)width + eps)) * g[0];
+    for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)o * ld_out + c] = cvt<OUT>(xr[c] * sc);
+}
+
+// ------------------------------------------------------------------------------------------------ input convolution
+// out_a = h + conv_a(h), out_b = h + conv_b(h); conv(h)_t = sum_j w[:, j] h_(t - taps + 1 + j).  Rows before the segment come from the
+// slot's history `tail` [n_slots][taps - 1][width] (zeros after a reset = zeros before the sequence's start).
+template <typename OT>
+__global__ void k_canon(PassTables t, const float* __restrict__ h, int width, int taps, const bf16* __restrict__ wa, const bf16* __restrict__ wb,
+                        const float* __restrict__ tail, OT* __restrict__ out_a, OT* __restrict__ out_b, int ld_out) {
+    const int r = blockIdx.x;
+    const int s = t.row_seg[r], row0 = t.seg_row0[s], slot = t.seg_slot[s];
+    const float* tl = tail + (size_t)slot * (taps - 1) * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float a = 0.0f, b = 0.0f;
+        for (int j = 0; j < taps; j++) {
+            const int src = r - (taps - 1) + j;
+            const float v = (src >= row0) ? h[(size_t)src * width + c] : tl[(size_t)(src - row0 + taps - 1) * width + c];
+            a += __bfloat162float(wa[(size_t)c * taps + j]) * v;
+            if (wb) b += __bfloat162float(wb[(size_t)c * taps + j]) * v;
+        }
+        const float hc = h[(size_t)r * width + c];
+        out_a[(size_t)r * ld_out + c] = cvt<OT>(hc + a);
+        if (out_b) out_b[(size_t)r * ld_out + c] = cvt<OT>(hc + b);
+    }
+}
+// no convolution configured: the operand is h itself
+template <typename OT>
+__global__ void k_copy_operand(const float* __restrict__ h, int width, OT* __restrict__ out_a, OT* __restrict__ out_b, int ld_out) {
+    const int r = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const OT v = cvt<OT>(h[(size_t)r * width + c]);
+        out_a[(size_t)r * ld_out + c] = v;
+        if (out_b) out_b[(size_t)r * ld_out + c] = v;
+    }
+}
+// history <- the last taps - 1 values of h of each segment's sequence.  One thread per channel walks k upwards: entry k is written
+// after every entry it is read for (k + len > k).
+__global__ void k_canon_tail(PassTables t, const float* __restrict__ h, int width, int taps, float* __restrict__ tail) {
+    const int s = blockIdx.x;
+    const int row0 = t.seg_row0[s], len = t.seg_len[s], slot = t.seg_slot[s];
+    if (t.slots[slot].stopped) return;
+    float* tl = tail + (size_t)slot * (taps - 1) * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        for (int k = 0; k < taps - 1; k++) {
+            const int off = len - (taps - 1) + k;          // offset inside the segment of the row that lands in entry k
+            tl[(size_t)k * width + c] = (off >= 0) ? h[(size_t)(row0 + off) * width + c] : tl[(size_t)(k + len) * width + c];
+        }
+}
+
+// ------------------------------------------------------------------------------------------------ matrix product (SIMT)
+// C[M][N] = (acc ? C : 0) + bias + A[M][K] . W[N][K]^T with fp32 accumulation on FFMA: the true-fp32 product, and the bf16 product of
+// passes too small for the tensor-core kernel.  K is a multiple of 16 (operands are zero-padded to a multiple of 64).
+constexpr int SG_BM = 64, SG_BN = 64, SG_BK = 16;
+template <typename AT>
+__global__ void __launch_bounds__(256) k_gemm_simt(const AT* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, float* __restrict__ C, int ldc,
+                                                   int M, int N, int K, const float* __restrict__ bias, int accumulate) {
+    __shared__ float sa[SG_BK][SG_BM + 4];
+    __shared__ float sw[SG_BK][SG_BN + 4];
+    const int m0 = blockIdx.y * SG_BM, n0 = blockIdx.x * SG_BN;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+    float acc[4][4] = {};
+    for (int k0 = 0; k0 < K; k0 += SG_BK) {
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int e = threadIdx.x + i * 256;          // 64 rows x 16 k
+            const int rr = e >> 4, kk = e & 15;
+            sa[kk][rr] = (m0 + rr < M) ? ldf<AT>(A + (size_t)(m0 + rr) * lda + k0 + kk) : 0.0f;
+            sw[kk][rr] = (n0 + rr < N) ? __bfloat162float(W[(size_t)(n0 + rr) * ldw + k0 + kk]) : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < SG_BK; kk++) {
+            float a[4], w[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) { a[i] = sa[kk][ty * 4 + i]; w[i] = sw[kk][tx * 4 + i]; }
+#pragma unroll
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int j = 0; j < 4; j++) acc[i][j] = fmaf(a[i], w[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const int m = m0 + ty * 4 + i;
+        if (m >= M) continue;
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int n = n0 + tx * 4 + j;
+            if (n >= N) continue;
+            float v = acc[i][j];
+            if (bias) v += bias[n];
+            if (accumulate) v += C[(size_t)m * ldc + n];
+            C[(size_t)m * ldc + n] = v;
+        }
+    }
+}
+
+// Few rows (decode): one warp per output column streams its weight row once for all M <= 8 rows; lanes split K.
+template <typename AT, int MR>
+__global__ void __launch_bounds__(256) k_gemv_rows(const AT* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, float* __restrict__ C, int ldc,
+                                                   int M, int N, int K, const float* __restrict__ bias, int accumulate) {
+    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (n >= N) return;
+    float acc[MR];
+#pragma unroll
+    for (int m = 0; m < MR; m++) acc[m] = 0.0f;
+    const bf16* w = W + (size_t)n * ldw;
+    for (int k = lane * 8; k < K; k += 256) {              // K % 64 == 0 and the rows are 16-byte aligned: 8 bf16 per load
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+        const bf16* wp = reinterpret_cast<const bf16*>(&wv);
+        float wf[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) wf[i] = __bfloat162float(wp[i]);
+#pragma unroll
+        for (int m = 0; m < MR; m++)
+            if (m < M) {
+                const AT* a = A + (size_t)m * lda + k;
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc[m] = fmaf(ldf<AT>(a + i), wf[i], acc[m]);
+            }
+    }
+#pragma unroll
+    for (int m = 0; m < MR; m++) {
+        if (m >= M) break;
+        float v = warp_sum(acc[m]);
+        if (lane == 0) {
+            if (bias) v += bias[n];
+            if (accumulate) v += C[(size_t)m * ldc + n];
+            C[(size_t)m * ldc + n] = v;
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ sigmoid attention
+struct AttnBranch {
+    int heads, kv_heads, dim, vdim;
+    float scale, eps, out_scale;
+    int qk_norm;
+    int q_off, k_off, v_off;     // column offsets of q | k | v in the projection buffer
+    int a_off;                   // column offset of this branch's output in the out-projection operand
+    const float* pb;             // [heads] or null
+    int max_ctx;
+};
+// q (and k) to unit RMS per head in place; k, v of every row appended to the slot's cache [n_slots][max_ctx][kv_heads * dim|vdim].
+template <typename OT>
+__global__ void k_attn_prep(PassTables t, AttnBranch b, float* __restrict__ P, int ldp, OT* __restrict__ kc, OT* __restrict__ vc) {
+    const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
+    float* p = P + (size_t)r * ldp;
+    const size_t crow = (size_t)slot * b.max_ctx + pos;
+    for (int u = wid; u < b.heads + 2 * b.kv_heads; u += nw) {
+        if (u < b.heads + b.kv_heads) {
+            const bool is_q = u < b.heads;
+            float* v = p + (is_q ? b.q_off + u * b.dim : b.k_off + (u - b.heads) * b.dim);
+            float sc = 1.0f;
+            if (b.qk_norm) {
+                float ss = 0.0f;
+                for (int i = lane; i < b.dim; i += 32) ss += v[i] * v[i];
+                ss = warp_sum(ss);
+                sc = 1.0f / sqrtf(ss / (float)b.dim + b.eps);
+            }
+            if (is_q) { for (int i = lane; i < b.dim; i += 32) v[i] *= sc; }
+            else {
+                OT* dst = kc + crow * (size_t)(b.kv_heads * b.dim) + (size_t)(u - b.heads) * b.dim;
+                for (int i = lane; i < b.dim; i += 32) dst[i] = cvt<OT>(v[i] * sc);
+            }
+        } else {
+            const int g = u - b.heads - b.kv_heads;
+            const float* v = p + b.v_off + g * b.vdim;
+            OT* dst = vc + crow * (size_t)(b.kv_heads * b.vdim) + (size_t)g * b.vdim;
+            for (int i = lane; i < b.vdim; i += 32) dst[i] = cvt<OT>(v[i]);
+        }
+    }
+}
+// one CTA per (row, query head): out = out_scale * sum_{j <= pos} sigmoid(scale q.k_j + pb) v_j, keys in tiles of blockDim.x.
+// A thread scores one key of the tile, then the threads turn to the value channels.  vdim <= 4 * blockDim.x.
+template <typename OT>
+__global__ void __launch_bounds__(128) k_sigattn(PassTables t, AttnBranch b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc,
+                                                 const OT* __restrict__ vc, OT* __restrict__ out, int ld_out) {
+    extern __shared__ float sm[];
+    float* sq = sm;                 // [dim]
+    float* swt = sm + b.dim;        // [blockDim.x]
+    const int r = blockIdx.x, h = blockIdx.y, g = h / (b.heads / b.kv_heads);
+    const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
+    const float* q = P + (size_t)r * ldp + b.q_off + h * b.dim;
+    for (int i = threadIdx.x; i < b.dim; i += blockDim.x) sq[i] = q[i];
+    const float bias = b.pb ? b.pb[h] : 0.0f;
+    const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
+    const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
+    const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    __syncthreads();
+    for (int j0 = 0; j0 <= pos; j0 += blockDim.x) {
+        const int j = j0 + threadIdx.x;
+        float w = 0.0f;
+        if (j <= pos) {
+            const OT* kr = kbase + (size_t)j * kld;
+            float s = 0.0f;
+            for (int i = 0; i < b.dim; i++) s = fmaf(sq[i], ldf<OT>(kr + i), s);
+            w = sigmoidf_(s * b.scale + bias);
+        }
+        swt[threadIdx.x] = w;
+        __syncthreads();
+        const int nj = min((int)blockDim.x, pos + 1 - j0);
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) {
+            const int c = threadIdx.x + cc * blockDim.x;
+            if (c < b.vdim) {
+                float a = acc[cc];
+                const OT* vr = vbase + (size_t)j0 * vld + c;
+                for (int jj = 0; jj < nj; jj++) a = fmaf(swt[jj], ldf<OT>(vr + (size_t)jj * vld), a);
+                acc[cc] = a;
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+        const int c = threadIdx.x + cc * blockDim.x;
+        if (c < b.vdim) out[(size_t)r * ld_out + b.a_off + h * b.vdim + c] = cvt<OT>(acc[cc] * b.out_scale);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ retention
+struct RetBranch {
+    int heads, dim, vdim;
+    float scale, eps, out_scale;
+    int rot_dims;
+    const float* inv_freq;       // [rot_dims / 2]
+    const float* decay;          // [heads]
+    int out_norm, gated;
+    int q_off, k_off, v_off, g_off;
+    int a_off;
+};
+// One CTA per (segment, head) walks the segment's rows in order: S <- decay S + k v^T, o = S^T q.  The state [dim][vdim] sits in shared
+// memory for the walk (thread = value channel; row groups of the state are split over the y dimension of the CTA and summed through
+// shared memory), starts from and returns to the slot's state in HBM.  q and k are rotated (pairs i, i + rot_dims/2) and k scaled here.
+// raw o goes to O [R][heads * vdim] (fp32); normalisation and the gate follow in k_ret_post.
+__global__ void k_retention(PassTables t, RetBranch b, const float* __restrict__ P, int ldp, float* __restrict__ state, float* __restrict__ O) {
+    extern __shared__ float sm[];
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int slot = t.seg_slot[s], row0 = t.seg_row0[s], len = t.seg_len[s];
+    const int ny = blockDim.y, ty = threadIdx.y, j = threadIdx.x;       // blockDim.x >= vdim
+    const int tid = ty * blockDim.x + j, nt = blockDim.x * ny;
+    float* S = sm;                                   // [dim][vdim]
+    float* sq = S + (size_t)b.dim * b.vdim;          // [2][dim]
+    float* sk = sq + 2 * b.dim;                      // [2][dim]
+    float* part = sk + 2 * b.dim;                    // [ny][vdim]
+    float* gs = state + ((size_t)slot * b.heads + h) * (size_t)b.dim * b.vdim;
+    const bool live = !t.slots[slot].stopped;
+    for (int i = tid; i < b.dim * b.vdim; i += nt) S[i] = gs[i];
+    const float decay = b.decay[h];
+    const int half = b.rot_dims / 2;
+    const int i0 = (int)(((long long)b.dim * ty) / ny), i1 = (int)(((long long)b.dim * (ty + 1)) / ny);
+    for (int n = 0; n < len; n++) {
+        const int r = row0 + n, buf = n & 1;
+        const float* p = P + (size_t)r * ldp;
+        const float pos = (float)t.row_pos[r];
+        for (int i = tid; i < b.dim; i += nt) {
+            float qv = p[b.q_off + h * b.dim + i], kv = p[b.k_off + h * b.dim + i];
+            if (i < b.rot_dims) {
+                const int f = i < half ? i : i - half;
+                float sn, cs;
+                sincosf(pos * b.inv_freq[f], &sn, &cs);
+                const int o = i < half ? i + half : i - half;
+                const float qo = p[b.q_off + h * b.dim + o], ko = p[b.k_off + h * b.dim + o];
+                // pair (u, v) = (x_i, x_(i + half)): u' = u cos - v sin, v' = v cos + u sin
+                qv = i < half ? qv * cs - qo * sn : qv * cs + qo * sn;
+                kv = i < half ? kv * cs - ko * sn : kv * cs + ko * sn;
+            }
+            sq[buf * b.dim + i] = qv;
+            sk[buf * b.dim + i] = kv * b.scale;
+        }
+        __syncthreads();
+        if (j < b.vdim) {
+            const float v = p[b.v_off + h * b.vdim + j];
+            float o = 0.0f;
+            for (int i = i0; i < i1; i++) {
+                const float sv = fmaf(decay, S[(size_t)i * b.vdim + j], sk[buf * b.dim + i] * v);
+                S[(size_t)i * b.vdim + j] = sv;
+                o = fmaf(sv, sq[buf * b.dim + i], o);
+            }
+            part[ty * b.vdim + j] = o;
+        }
+        __syncthreads();
+        if (ty == 0 && j < b.vdim) {
+            float o = 0.0f;
+            for (int y = 0; y < ny; y++) o += part[y * b.vdim + j];
+            O[(size_t)r * (b.heads * b.vdim) + h * b.vdim + j] = o;
+        }
+    }
+    __syncthreads();
+    if (live)
+        for (int i = tid; i < b.dim * b.vdim; i += nt) gs[i] = S[i];
+}
+// per (row, head): o / rms(o) (optional), * silu(gate) (optional), * out_scale -> operand of the out projection
+template <typename OT>
+__global__ void k_ret_post(RetBranch b, const float* __restrict__ O, const float* __restrict__ P, int ldp, OT* __restrict__ out, int ld_out) {
+    const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    for (int h = wid; h < b.heads; h += nw) {
+        const float* o = O + (size_t)r * (b.heads * b.vdim) + h * b.vdim;
+        float sc = b.out_scale;
+        if (b.out_norm) {
+            float ss = 0.0f;
+            for (int i = lane; i < b.vdim; i += 32) ss += o[i] * o[i];
+            ss = warp_sum(ss);
+            sc *= 1.0f / sqrtf(ss / (float)b.vdim + b.eps);
+        }
+        for (int i = lane; i < b.vdim; i += 32) {
+            float v = o[i] * sc;
+            if (b.gated) { const float g = P[(size_t)r * ldp + b.g_off + h * b.vdim + i]; v *= g * sigmoidf_(g); }
+            out[(size_t)r * ld_out + b.a_off + h * b.vdim + i] = cvt<OT>(v);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ feed-forward activation, glue
+// act = gelu_tanh(gate) * up from G [R][2 ff] (gate | up) into the out-projection operand at column a_off
+template <typename OT>
+__global__ void k_geglu(const float* __restrict__ G, int ff, OT* __restrict__ out, int ld_out, int a_off, int R) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)R * ff) return;
+    const int r = (int)(i / ff), c = (int)(i % ff);
+    out[(size_t)r * ld_out + a_off + c] = cvt<OT>(gelu_tanh(G[(size_t)r * 2 * ff + c]) * G[(size_t)r * 2 * ff + ff + c]);
+}
+// operand [x | x0] of the loop's entry projection
+template <typename OT>
+__global__ void k_concat2(const float* __restrict__ x, const float* __restrict__ x0, int width, OT* __restrict__ out, int ld_out) {
+    const int r = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        out[(size_t)r * ld_out + c] = cvt<OT>(x[(size_t)r * width + c]);
+        out[(size_t)r * ld_out + width + c] = cvt<OT>(x0[(size_t)r * width + c]);
+    }
+}
+
+// ------------------------------------------------------------------------------------------------ sampling
+// first maximum of each logits row (lowest index wins ties, like the greedy loop of the single-model engine); the token becomes the
+// slot's pending token and lands in hist[row][step]; a slot that samples eos_id stops.
+__global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ logits, int n, PassTables t, int eos_id, int* __restrict__ out,
+                                                       int out_ld, int out_col) {
+    __shared__ float sv[32];
+    __shared__ int si[32];
+    const int s = blockIdx.x, tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const float* lg = logits + (size_t)s * n;
+    float best = -INFINITY;
+    int arg = 0x7fffffff;
+    for (int j = tid; j < n; j += blockDim.x) {
+        const float v = lg[j];
+        if (v > best) { best = v; arg = j; }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+        if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
+    }
+    if (lane == 0) { sv[wid] = best; si[wid] = arg; }
+    __syncthreads();
+    if (wid == 0) {
+        best = sv[lane]; arg = si[lane];
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
+        }
+        if (lane == 0) {
+            if (arg == 0x7fffffff) arg = 0;
+            SlotState& st = t.slots[t.seg_slot[s]];
+            if (st.stopped) arg = st.pending;
+            st.pending = arg;
+            if (eos_id >= 0 && arg == eos_id) st.stopped = 1;
+            out[(size_t)s * out_ld + out_col] = arg;
+        }
+    }
+}
+
+}  // namespace seq
+}  // namespace gtb
