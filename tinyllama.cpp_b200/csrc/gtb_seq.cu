@@ -33,6 +33,7 @@ struct TensorDest {
     int rows = 0, cols = 0;    // expected logical shape ([rows] for vectors with cols == 0)
     int ld = 0;                // destination row stride in elements (matrix)
     bool scalar = false;       // shape []
+    int group = 0, group_stride = 0;   // matrix rows placed in groups of `group` rows, `group_stride` rows apart (0: contiguous)
     bool loaded = false;
 };
 
@@ -54,6 +55,7 @@ struct LayerW {
     int ff = 0;
     bf16 *w_mix = nullptr, *w_gu = nullptr, *w_out = nullptr, *canon_a = nullptr, *canon_b = nullptr;
     float* d_gain = nullptr;
+    bool gu_inter = false;     // gate and up rows interleaved in groups of 32 (what the fused tensor-core epilogue reads)
 };
 
 struct Run {
@@ -81,6 +83,8 @@ struct gtb_seq_model {
     int max_rows = 0, n1_max = 0, ff_max = 0, kout_p_max = 0, ro_max = 0;
     float *x = nullptr, *x0 = nullptr, *h = nullptr, *P = nullptr, *G = nullptr, *O = nullptr, *logits = nullptr;
     void *opA = nullptr, *opB = nullptr, *opC = nullptr, *opL = nullptr, *opH = nullptr;
+    float* retU = nullptr;                       // chunked retention: per-chunk contributions / states [chunks][heads][dim][vdim]
+    size_t retU_floats = 0;
     float* cap = nullptr;                        // [runs][max_rows][width]
     bool capture = false;
     int cap_rows = 0;
@@ -166,6 +170,35 @@ RetBranch ret_args(const gtb_seq_model* m, const BranchW& b) {
     return a;
 }
 
+// chunked retention (prompt portions): chunk length, value-slice width and shared memory of its two matrix kernels
+struct RetChunk { int C, vs; size_t smem_kv, smem_out; bool ok; };
+RetChunk ret_chunk(const gtb_seq_branch& d) {
+    RetChunk r;
+    r.C = d.dim <= 128 ? 64 : 32;
+    r.vs = std::min(d.vdim, 64);
+    r.smem_kv = ((size_t)r.C * (d.dim + 1) + (size_t)r.C * r.vs) * sizeof(float);
+    r.smem_out = (2 * (size_t)r.C * (d.dim + 1) + (size_t)r.C * r.vs + (size_t)r.C * (r.C + 1) + (size_t)d.dim * r.vs) * sizeof(float);
+    r.ok = r.smem_out <= 200 * 1024;
+    return r;
+}
+
+template <int DP, int VP>
+int launch_sigattn_mma(const PassTables& t, const AttnBranch& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, bf16* out, int ld_out) {
+    const size_t smem = (2 * 64 * (size_t)(DP + 8) + 64 * (size_t)(VP + 8)) * 2;
+    static bool attr = false;
+    if (!attr) { GTB_CUDA(cudaFuncSetAttribute(k_sigattn_mma<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
+    k_sigattn_mma<DP, VP><<<dim3(n_tiles, a.heads), 128, smem, ctx().stream>>>(t, a, S, P, ldp, kc, vc, out, ld_out);
+    GTB_LAUNCHED();
+    return GTB_OK;
+}
+int sigattn_mma(const PassTables& t, const AttnBranch& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, bf16* out, int ld_out) {
+    const int dp = a.dim <= 32 ? 32 : a.dim <= 64 ? 64 : 128, vp = a.vdim <= 32 ? 32 : a.vdim <= 64 ? 64 : 128;
+#define SA_CASE(D, V) if (dp == D && vp == V) return launch_sigattn_mma<D, V>(t, a, S, n_tiles, P, ldp, kc, vc, out, ld_out)
+    SA_CASE(32, 32); SA_CASE(32, 64); SA_CASE(32, 128); SA_CASE(64, 32); SA_CASE(64, 64); SA_CASE(64, 128); SA_CASE(128, 32); SA_CASE(128, 64); SA_CASE(128, 128);
+#undef SA_CASE
+    return -1;
+}
+
 struct RetLaunch { dim3 block; size_t smem; };
 RetLaunch ret_launch(const gtb_seq_branch& d) {
     RetLaunch r;
@@ -178,11 +211,15 @@ RetLaunch ret_launch(const gtb_seq_branch& d) {
 
 // the launch sequence of one pass: R rows of S segments whose tables are already on the device
 template <typename OT>
-int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pending, int n_want, const int* d_want) {
+int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pending, int n_want, const int* d_want, const int* seg_lens = nullptr) {
     cudaStream_t st = ctx().stream;
     const gtb_seq_config& c = m->cfg;
     const int W = c.width, wp = m->wp;
     OT *opA = (OT*)m->opA, *opB = (OT*)m->opB, *opC = (OT*)m->opC, *opL = (OT*)m->opL, *opH = (OT*)m->opH;
+    // prompt portions (the host knows the segment lengths and they are long on average) take the tiled kernels of the mixers
+    const bool portions = seg_lens != nullptr && m->fused_attn && R >= 16 * S;
+    int n_qtiles = 0;
+    if (portions) for (int s = 0; s < S; s++) n_qtiles += (seg_lens[s] + 63) / 64;
     k_plan<<<(R + 127) / 128, 128, 0, st>>>(t, R, from_pending ? 1 : 0);
     GTB_LAUNCHED();
     k_embed<<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, m->x, c.loop_times > 0 ? m->x0 : nullptr);
@@ -212,9 +249,18 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
         }
         int rc = product<OT>(m, opA, wp, l.w_mix, wp, m->P, l.n1, R, l.n1, wp, nullptr, 0);
         if (rc) return rc;
+        bool ff_done = false;
         if (l.ff > 0) {
-            rc = product<OT>(m, opB, wp, l.w_gu, wp, m->G, 2 * l.ff, R, 2 * l.ff, wp, nullptr, 0);
-            if (rc) return rc;
+            // tensor-core pass: gelu(gate) * up comes out of the product's epilogue as the out-projection operand
+            if (sizeof(OT) == 2 && m->use_tensor && m->gp && R >= m->tensor_min_rows && l.gu_inter) {
+                rc = seq_gemm_bf16_geglu(m->gp, opB, wp, l.w_gu, wp, opC, l.kout_p, l.kout - l.ff, R, 2 * l.ff, wp);
+                if (rc > 0) return rc;
+                if (rc == 0) { ctx().launches++; ff_done = true; }
+            }
+            if (!ff_done) {
+                rc = product<OT>(m, opB, wp, l.w_gu, wp, m->G, 2 * l.ff, R, 2 * l.ff, wp, nullptr, 0);
+                if (rc) return rc;
+            }
         }
         for (int bi = 0; bi < l.d.n_branches; bi++) {
             const BranchW& b = l.br[bi];
@@ -222,10 +268,37 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                 const AttnBranch a = attn_args(m, b);
                 k_attn_prep<OT><<<R, 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[bi], (OT*)run.vc[bi]);
                 GTB_LAUNCHED();
-                k_sigattn<OT><<<dim3(R, a.heads), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], opC, l.kout_p);
-                GTB_LAUNCHED();
+                int done = -1;
+                if (portions && sizeof(OT) == 2 && a.dim <= 128 && a.vdim <= 128)
+                    done = sigattn_mma(t, a, S, n_qtiles, m->P, l.n1, (const bf16*)run.kc[bi], (const bf16*)run.vc[bi], (bf16*)opC, l.kout_p);
+                if (done > 0) return done;
+                if (done < 0) {
+                    k_sigattn<OT><<<dim3(R, a.heads), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], opC, l.kout_p);
+                    GTB_LAUNCHED();
+                }
             } else {
                 const RetBranch a = ret_args(m, b);
+                const RetChunk rcfg = ret_chunk(b.d);
+                if (portions && rcfg.ok) {
+                    int n_chunks = 0;
+                    for (int s = 0; s < S; s++) n_chunks += (seg_lens[s] + rcfg.C - 1) / rcfg.C;
+                    const size_t need = (size_t)n_chunks * a.heads * a.dim * a.vdim;
+                    if (need > m->retU_floats) return gtb::fail(GTB_ERR_STATE, "chunk workspace too small (%zu > %zu floats)", need, m->retU_floats);
+                    const int nvs = (a.vdim + rcfg.vs - 1) / rcfg.vs;
+                    k_ret_rotate<<<R, 128, 0, st>>>(t, a, m->P, l.n1);
+                    GTB_LAUNCHED();
+                    if (rcfg.smem_kv > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_ret_chunk_kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rcfg.smem_kv));
+                    k_ret_chunk_kv<<<dim3(n_chunks, a.heads, nvs), 256, rcfg.smem_kv, st>>>(t, a, m->P, l.n1, S, rcfg.C, rcfg.vs, m->retU);
+                    GTB_LAUNCHED();
+                    k_ret_scan<<<dim3(S, a.heads), 256, 0, st>>>(t, a, S, rcfg.C, m->retU, run.state[bi]);
+                    GTB_LAUNCHED();
+                    if (rcfg.smem_out > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_ret_chunk_out, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rcfg.smem_out));
+                    k_ret_chunk_out<<<dim3(n_chunks, a.heads, nvs), 256, rcfg.smem_out, st>>>(t, a, m->P, l.n1, S, rcfg.C, rcfg.vs, m->retU, m->O);
+                    GTB_LAUNCHED();
+                    k_ret_post<OT><<<R, 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
+                    GTB_LAUNCHED();
+                    continue;
+                }
                 const RetLaunch rl = ret_launch(b.d);
                 if (rl.smem > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_retention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rl.smem));
                 k_retention<<<dim3(S, a.heads), rl.block, rl.smem, st>>>(t, a, m->P, l.n1, run.state[bi], m->O);
@@ -234,9 +307,9 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                 GTB_LAUNCHED();
             }
         }
-        if (l.ff > 0) {
+        if (l.ff > 0 && !ff_done) {
             const size_t n = (size_t)R * l.ff;
-            k_geglu<OT><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(m->G, l.ff, opC, l.kout_p, l.kout - l.ff, R);
+            k_geglu<OT><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(m->G, l.ff, opC, l.kout_p, l.kout - l.ff, R, l.gu_inter ? 1 : 0);
             GTB_LAUNCHED();
         }
         rc = product<OT>(m, opC, l.kout_p, l.w_out, l.kout_p, m->x, W, R, W, l.kout_p, nullptr, 1);
@@ -361,8 +434,11 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
         }
         if (l.ff > 0) {
             TRY(dalloc_t(m, &l.w_gu, (size_t)2 * l.ff * wp));
+            l.gu_inter = l.ff % 32 == 0;
             want_matrix(m, lp + "mlp.gate", l.w_gu, l.ff, W, wp);
-            want_matrix(m, lp + "mlp.up", l.w_gu + (size_t)l.ff * wp, l.ff, W, wp);
+            want_matrix(m, lp + "mlp.up", l.w_gu + (size_t)(l.gu_inter ? 32 : l.ff) * wp, l.ff, W, wp);
+            if (l.gu_inter)
+                for (const char* nm : {"mlp.gate", "mlp.up"}) { TensorDest& d = m->tensors[lp + nm]; d.group = 32; d.group_stride = 64; }
             want_matrix(m, lp + "mlp.down", l.w_out + ko, W, l.ff, l.kout_p);
         }
         TRY(dalloc_t(m, &l.d_gain, 1));
@@ -423,6 +499,14 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     TRY(dalloc_t(m, &m->P, R * m->n1_max));
     TRY(dalloc_t(m, &m->G, R * 2 * std::max(m->ff_max, 1)));
     TRY(dalloc_t(m, &m->O, R * std::max(m->ro_max, 1)));
+    for (const LayerW& l : m->L)
+        for (int bi = 0; bi < l.d.n_branches; bi++)
+            if (l.br[bi].d.kind == GTB_MIX_RETENTION && ret_chunk(l.br[bi].d).ok) {
+                const gtb_seq_branch& d = l.br[bi].d;
+                const size_t chunks = R / ret_chunk(d).C + c.n_slots + 1;
+                m->retU_floats = std::max(m->retU_floats, chunks * d.heads * d.dim * d.vdim);
+            }
+    if (m->retU_floats) TRY(dalloc_t(m, &m->retU, m->retU_floats));
     TRY(dalloc_t(m, &m->logits, R * c.vocab));
     TRY(dalloc(m, &m->opA, R * wp * es));
     TRY(dalloc(m, &m->opB, R * wp * es));
@@ -470,7 +554,13 @@ int gtb_seq_set_tensor(gtb_seq_t m, const char* name, const void* h_bf16, const 
     else ok = ndim == 2 && r == d.rows && cc == d.cols;
     if (!ok) return gtb::fail(GTB_ERR_ARG, "tensor '%s': shape does not fit the description (expected [%d, %d])", name, d.rows, d.cols);
     if (d.kind == 0) {
-        GTB_CUDA(cudaMemcpy2D(d.dst, (size_t)d.ld * 2, h_bf16, (size_t)d.cols * 2, (size_t)d.cols * 2, d.rows, cudaMemcpyHostToDevice));
+        if (d.group > 0) {
+            for (int r0 = 0; r0 < d.rows; r0 += d.group)
+                GTB_CUDA(cudaMemcpy2D((bf16*)d.dst + (size_t)(r0 / d.group) * d.group_stride * d.ld, (size_t)d.ld * 2,
+                                      (const bf16*)h_bf16 + (size_t)r0 * d.cols, (size_t)d.cols * 2, (size_t)d.cols * 2, std::min(d.group, d.rows - r0), cudaMemcpyHostToDevice));
+        } else {
+            GTB_CUDA(cudaMemcpy2D(d.dst, (size_t)d.ld * 2, h_bf16, (size_t)d.cols * 2, (size_t)d.cols * 2, d.rows, cudaMemcpyHostToDevice));
+        }
     } else {
         const size_t n = d.scalar ? 1 : (size_t)d.rows * std::max(d.cols, 1);
         std::vector<float> f(n);
@@ -585,8 +675,8 @@ static int step_impl(gtb_seq_t m, int n_seg, const int32_t* seg_slot, const int3
         int rc;
         // greedy passes: logits rows are ordered like greedy_segs; the argmax kernel needs a segment per logits row, so it runs on
         // a table of its own below
-        if (c.mode == GTB_SEQ_F32) rc = run_pass<float>(m, t, R, S, false, nw, d_want);
-        else rc = run_pass<bf16>(m, t, R, S, false, nw, d_want);
+        if (c.mode == GTB_SEQ_F32) rc = run_pass<float>(m, t, R, S, false, nw, d_want, pl.data());
+        else rc = run_pass<bf16>(m, t, R, S, false, nw, d_want, pl.data());
         if (rc) return rc;
         if (greedy && nw) {
             // segment table restricted to the segments that ended: reuse the upload buffer behind the pass's tables
@@ -613,6 +703,12 @@ static int step_impl(gtb_seq_t m, int n_seg, const int32_t* seg_slot, const int3
         seg = s; off = o;
     }
     (void)next;
+    if (m->gp) {
+        int bad = 0;
+        int rc = seq_gemm_status(m->gp, &bad);
+        if (rc) return rc;
+        if (bad) return gtb::fail(GTB_ERR_STATE, "a tensor-core product gave up on a pipeline wait; results of this step are not valid");
+    }
     return GTB_OK;
 }
 

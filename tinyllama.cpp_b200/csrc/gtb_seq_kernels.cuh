@@ -438,13 +438,15 @@ __global__ void k_ret_post(RetBranch b, const float* __restrict__ O, const float
 }
 
 // ------------------------------------------------------------------------------------------------ feed-forward activation, glue
-// act = gelu_tanh(gate) * up from G [R][2 ff] (gate | up) into the out-projection operand at column a_off
+// act = gelu_tanh(gate) * up from G [R][2 ff] into the out-projection operand at column a_off.  Columns of G: gate | up, or
+// (interleaved) groups of 32 gate columns each followed by its 32 up columns.
 template <typename OT>
-__global__ void k_geglu(const float* __restrict__ G, int ff, OT* __restrict__ out, int ld_out, int a_off, int R) {
+__global__ void k_geglu(const float* __restrict__ G, int ff, OT* __restrict__ out, int ld_out, int a_off, int R, int interleaved) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= (size_t)R * ff) return;
     const int r = (int)(i / ff), c = (int)(i % ff);
-    out[(size_t)r * ld_out + a_off + c] = cvt<OT>(gelu_tanh(G[(size_t)r * 2 * ff + c]) * G[(size_t)r * 2 * ff + ff + c]);
+    const int gc = interleaved ? (c >> 5) * 64 + (c & 31) : c, uc = interleaved ? gc + 32 : ff + c;
+    out[(size_t)r * ld_out + a_off + c] = cvt<OT>(gelu_tanh(G[(size_t)r * 2 * ff + gc]) * G[(size_t)r * 2 * ff + uc]);
 }
 // operand [x | x0] of the loop's entry projection
 template <typename OT>
@@ -492,6 +494,313 @@ __global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ 
             st.pending = arg;
             if (eos_id >= 0 && arg == eos_id) st.stopped = 1;
             out[(size_t)s * out_ld + out_col] = arg;
+        }
+    }
+}
+
+// ================================================================================================ chunked retention (prompt portions)
+// The recurrence S_t = g S_(t-1) + k_t v_t^T, o_t = S_t^T q_t over a chunk of L rows that starts from state S0 is
+//     o_a   = g^(a+1) S0^T q_a + sum_{b <= a} g^(a-b) (q_a . k_b) v_b
+//     S_end = g^L S0 + sum_b g^(L-1-b) k_b v_b^T
+// so the rows of a chunk are matrix products, and only a cheap scan over the chunks' [dim][vdim] contributions is sequential:
+//   k_ret_rotate     rotary positions on q and k, k scaled (in place, fp32)
+//   k_ret_chunk_kv   U_c = sum_b g^(L-1-b) k_b v_b^T for every chunk, all chunks in parallel
+//   k_ret_scan       per (segment, head): walks the chunks, leaves the state BEFORE each chunk in its U_c slot, writes the slot's state
+//   k_ret_chunk_out  o of every row from its chunk's q, k, v and the state before the chunk, all chunks in parallel
+// All of it is fp32 FFMA in both compute modes: state, decay powers and everything that enters the recurrence stay in 32-bit.
+__device__ __forceinline__ bool ret_find_chunk(const PassTables& t, int S, int C, int idx, int& seg, int& c) {
+    for (int s = 0; s < S; s++) {
+        const int n = (t.seg_len[s] + C - 1) / C;
+        if (idx < n) { seg = s; c = idx; return true; }
+        idx -= n;
+    }
+    return false;
+}
+
+__global__ void k_ret_rotate(PassTables t, RetBranch b, float* __restrict__ P, int ldp) {
+    const int r = blockIdx.x;
+    float* p = P + (size_t)r * ldp;
+    const float pos = (float)t.row_pos[r];
+    const int half = b.rot_dims / 2;
+    for (int e = threadIdx.x; e < b.heads * b.dim; e += blockDim.x) {
+        const int h = e / b.dim, i = e % b.dim;
+        if (i < half) {
+            float sn, cs;
+            sincosf(pos * b.inv_freq[i], &sn, &cs);
+            float* q = p + b.q_off + h * b.dim;
+            float* k = p + b.k_off + h * b.dim;
+            const float qu = q[i], qv = q[i + half], ku = k[i], kv = k[i + half];
+            q[i] = qu * cs - qv * sn; q[i + half] = qv * cs + qu * sn;
+            k[i] = (ku * cs - kv * sn) * b.scale; k[i + half] = (kv * cs + ku * sn) * b.scale;
+        } else if (i >= b.rot_dims) {
+            p[b.k_off + h * b.dim + i] *= b.scale;
+        }
+    }
+}
+
+// grid (chunks, heads, value slices); U [chunk][head][dim][vdim]
+__global__ void __launch_bounds__(256) k_ret_chunk_kv(PassTables t, RetBranch b, const float* __restrict__ P, int ldp, int S, int C, int vs,
+                                                      float* __restrict__ U) {
+    extern __shared__ float sm[];
+    int seg, c;
+    if (!ret_find_chunk(t, S, C, blockIdx.x, seg, c)) return;
+    const int h = blockIdx.y, j0 = blockIdx.z * vs, nv = min(vs, b.vdim - j0);
+    const int row0 = t.seg_row0[seg] + c * C, L = min(C, t.seg_len[seg] - c * C);
+    float* sk = sm;                       // [C][dim + 1], already times g^(L-1-b)
+    float* sv = sm + C * (b.dim + 1);     // [C][vs]
+    const float lg = logf(b.decay[h]);
+    for (int e = threadIdx.x; e < L * b.dim; e += blockDim.x) {
+        const int bb = e / b.dim, i = e % b.dim;
+        sk[bb * (b.dim + 1) + i] = P[(size_t)(row0 + bb) * ldp + b.k_off + h * b.dim + i] * expf(lg * (float)(L - 1 - bb));
+    }
+    for (int e = threadIdx.x; e < L * nv; e += blockDim.x) {
+        const int bb = e / nv, j = e % nv;
+        sv[bb * vs + j] = P[(size_t)(row0 + bb) * ldp + b.v_off + h * b.vdim + j0 + j];
+    }
+    __syncthreads();
+    float* u = U + (((size_t)blockIdx.x * b.heads + h) * b.dim) * b.vdim;
+    const int tj = (nv + 3) / 4, ti = (b.dim + 3) / 4;
+    for (int tile = threadIdx.x; tile < ti * tj; tile += blockDim.x) {
+        const int i4 = (tile / tj) * 4, j4 = (tile % tj) * 4;
+        float acc[4][4] = {};
+        for (int bb = 0; bb < L; bb++) {
+            float kk[4], vv[4];
+#pragma unroll
+            for (int x = 0; x < 4; x++) { kk[x] = (i4 + x < b.dim) ? sk[bb * (b.dim + 1) + i4 + x] : 0.0f; vv[x] = (j4 + x < nv) ? sv[bb * vs + j4 + x] : 0.0f; }
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+#pragma unroll
+                for (int y = 0; y < 4; y++) acc[x][y] = fmaf(kk[x], vv[y], acc[x][y]);
+        }
+#pragma unroll
+        for (int x = 0; x < 4; x++)
+#pragma unroll
+            for (int y = 0; y < 4; y++)
+                if (i4 + x < b.dim && j4 + y < nv) u[(size_t)(i4 + x) * b.vdim + j0 + j4 + y] = acc[x][y];
+    }
+}
+
+// grid (segments, heads): element-parallel scan over the segment's chunks
+__global__ void __launch_bounds__(256) k_ret_scan(PassTables t, RetBranch b, int S, int C, float* __restrict__ U, float* __restrict__ state) {
+    const int seg = blockIdx.x, h = blockIdx.y;
+    int first = 0;
+    for (int s = 0; s < seg; s++) first += (t.seg_len[s] + C - 1) / C;
+    const int len = t.seg_len[seg], nchunk = (len + C - 1) / C, slot = t.seg_slot[seg];
+    float* gs = state + ((size_t)slot * b.heads + h) * (size_t)b.dim * b.vdim;
+    const float lg = logf(b.decay[h]);
+    const bool live = !t.slots[slot].stopped;
+    for (int e = threadIdx.x; e < b.dim * b.vdim; e += blockDim.x) {
+        float s0 = gs[e];
+        for (int c = 0; c < nchunk; c++) {
+            float* u = U + (((size_t)(first + c) * b.heads + h) * b.dim) * b.vdim + e;
+            const float add = *u;
+            *u = s0;
+            s0 = fmaf(expf(lg * (float)min(C, len - c * C)), s0, add);
+        }
+        if (live) gs[e] = s0;
+    }
+}
+
+// grid (chunks, heads, value slices); Sb [chunk][head][dim][vdim] = state before the chunk; O [R][heads * vdim]
+__global__ void __launch_bounds__(256) k_ret_chunk_out(PassTables t, RetBranch b, const float* __restrict__ P, int ldp, int S, int C, int vs,
+                                                       const float* __restrict__ Sb, float* __restrict__ O) {
+    extern __shared__ float sm[];
+    int seg, c;
+    if (!ret_find_chunk(t, S, C, blockIdx.x, seg, c)) return;
+    const int h = blockIdx.y, j0 = blockIdx.z * vs, nv = min(vs, b.vdim - j0);
+    const int row0 = t.seg_row0[seg] + c * C, L = min(C, t.seg_len[seg] - c * C);
+    const int ldq = b.dim + 1;
+    float* sq = sm;                       // [C][dim + 1]
+    float* sk = sq + C * ldq;             // [C][dim + 1]
+    float* sv = sk + C * ldq;             // [C][vs]
+    float* sa = sv + C * vs;              // [C][C + 1]
+    float* s0 = sa + C * (C + 1);         // [dim][vs]
+    const float lg = logf(b.decay[h]);
+    for (int e = threadIdx.x; e < L * b.dim; e += blockDim.x) {
+        const int bb = e / b.dim, i = e % b.dim;
+        const float* p = P + (size_t)(row0 + bb) * ldp;
+        sq[bb * ldq + i] = p[b.q_off + h * b.dim + i];
+        sk[bb * ldq + i] = p[b.k_off + h * b.dim + i];
+    }
+    for (int e = threadIdx.x; e < L * nv; e += blockDim.x) {
+        const int bb = e / nv, j = e % nv;
+        sv[bb * vs + j] = P[(size_t)(row0 + bb) * ldp + b.v_off + h * b.vdim + j0 + j];
+    }
+    const float* sb = Sb + (((size_t)blockIdx.x * b.heads + h) * b.dim) * b.vdim;
+    for (int e = threadIdx.x; e < b.dim * nv; e += blockDim.x) {
+        const int i = e / nv, j = e % nv;
+        s0[i * vs + j] = sb[(size_t)i * b.vdim + j0 + j];
+    }
+    __syncthreads();
+    // A[a][bb] = g^(a - bb) q_a . k_bb for bb <= a
+    for (int e = threadIdx.x; e < L * L; e += blockDim.x) {
+        const int a = e / L, bb = e % L;
+        float d = 0.0f;
+        if (bb <= a) {
+            for (int i = 0; i < b.dim; i++) d = fmaf(sq[a * ldq + i], sk[bb * ldq + i], d);
+            d *= expf(lg * (float)(a - bb));
+        }
+        sa[a * (C + 1) + bb] = d;
+    }
+    __syncthreads();
+    // o[a][j] = sum_bb A[a][bb] v[bb][j] + g^(a+1) sum_i q[a][i] S0[i][j]; a thread owns 4 consecutive rows of one value channel
+    const int ta = (L + 3) / 4;
+    for (int tile = threadIdx.x; tile < ta * nv; tile += blockDim.x) {
+        const int a4 = (tile / nv) * 4, j = tile % nv;
+        float intra[4] = {0, 0, 0, 0}, inter[4] = {0, 0, 0, 0};
+        const int bmax = min(L, a4 + 4);
+        for (int bb = 0; bb < bmax; bb++) {
+            const float v = sv[bb * vs + j];
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+                if (a4 + x < L) intra[x] = fmaf(sa[(a4 + x) * (C + 1) + bb], v, intra[x]);
+        }
+        for (int i = 0; i < b.dim; i++) {
+            const float s = s0[i * vs + j];
+#pragma unroll
+            for (int x = 0; x < 4; x++)
+                if (a4 + x < L) inter[x] = fmaf(sq[(a4 + x) * ldq + i], s, inter[x]);
+        }
+#pragma unroll
+        for (int x = 0; x < 4; x++)
+            if (a4 + x < L) O[(size_t)(row0 + a4 + x) * (b.heads * b.vdim) + h * b.vdim + j0 + j] = fmaf(expf(lg * (float)(a4 + x + 1)), inter[x], intra[x]);
+    }
+}
+
+// ================================================================================================ sigmoid attention on tensor cores
+// Prompt portions in bf16 mode: a CTA owns 64 consecutive rows of one segment and one query head (4 warps x 16 rows) and sweeps the
+// slot's cache in tiles of 64 keys up to its last row's position: S = Q K^T on mma.sync m16n8k16 (bf16 operands, fp32 accumulators),
+// weight = sigmoid(scale S + pb) in fp32 under the causal mask, O += W V with the weights as bf16 A fragments taken straight from
+// the accumulator registers.  No running maximum and no rescaling: the weights are not normalised.  DP / VP: head sizes padded to
+// 32, 64 or 128 with zero columns in shared memory.
+__device__ __forceinline__ void sa_ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void sa_ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void sa_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t sa_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ bool sa_find_tile(const PassTables& t, int S, int idx, int& seg, int& q0) {
+    for (int s = 0; s < S; s++) {
+        const int n = (t.seg_len[s] + 63) / 64;
+        if (idx < n) { seg = s; q0 = idx * 64; return true; }
+        idx -= n;
+    }
+    return false;
+}
+
+template <int DP, int VP>
+__global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b, int S, const float* __restrict__ P, int ldp, const bf16* __restrict__ kc,
+                                                     const bf16* __restrict__ vc, bf16* __restrict__ out, int ld_out) {
+    constexpr int LQ = DP + 8, LV = VP + 8;
+    extern __shared__ __align__(16) unsigned char sa_raw[];
+    bf16* sq = reinterpret_cast<bf16*>(sa_raw);          // [64][LQ]
+    bf16* sk = sq + 64 * LQ;                            // [64][LQ]
+    bf16* sv = sk + 64 * LQ;                            // [64][LV]
+    int seg, q0;
+    if (!sa_find_tile(t, S, blockIdx.x, seg, q0)) return;
+    const int h = blockIdx.y, g = h / (b.heads / b.kv_heads);
+    const int slot = t.seg_slot[seg], row0 = t.seg_row0[seg] + q0, nq = min(64, t.seg_len[seg] - q0);
+    const int pos0 = t.row_pos[row0];                    // position of the tile's first row; row i sits at pos0 + i
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    for (int e = threadIdx.x; e < 64 * DP; e += 128) {
+        const int r = e / DP, i = e % DP;
+        sq[r * LQ + i] = __float2bfloat16_rn((r < nq && i < b.dim) ? P[(size_t)(row0 + r) * ldp + b.q_off + h * b.dim + i] : 0.0f);
+    }
+    const float bias = b.pb ? b.pb[h] : 0.0f;
+    const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
+    const bf16* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
+    const bf16* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
+    const bool vec = (b.dim % 8 == 0) && (b.vdim % 8 == 0);
+    float o[VP / 8][4];
+#pragma unroll
+    for (int n = 0; n < VP / 8; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    const int last = pos0 + nq - 1;                      // last key any row of the tile sees
+    const uint32_t sq_a = (uint32_t)__cvta_generic_to_shared(sq), sk_a = (uint32_t)__cvta_generic_to_shared(sk), sv_a = (uint32_t)__cvta_generic_to_shared(sv);
+    for (int j0 = 0; j0 <= last; j0 += 64) {
+        __syncthreads();                                 // the previous tile's fragments have been read
+        const int nk = min(64, last + 1 - j0);
+        if (vec) {
+            for (int e = threadIdx.x; e < 64 * (DP / 8); e += 128) {
+                const int r = e / (DP / 8), c8 = (e % (DP / 8)) * 8;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (r < nk && c8 < b.dim) v = *reinterpret_cast<const uint4*>(kbase + (size_t)(j0 + r) * kld + c8);
+                *reinterpret_cast<uint4*>(sk + r * LQ + c8) = v;
+            }
+            for (int e = threadIdx.x; e < 64 * (VP / 8); e += 128) {
+                const int r = e / (VP / 8), c8 = (e % (VP / 8)) * 8;
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (r < nk && c8 < b.vdim) v = *reinterpret_cast<const uint4*>(vbase + (size_t)(j0 + r) * vld + c8);
+                *reinterpret_cast<uint4*>(sv + r * LV + c8) = v;
+            }
+        } else {
+            for (int e = threadIdx.x; e < 64 * DP; e += 128) {
+                const int r = e / DP, i = e % DP;
+                sk[r * LQ + i] = (r < nk && i < b.dim) ? kbase[(size_t)(j0 + r) * kld + i] : __float2bfloat16_rn(0.0f);
+            }
+            for (int e = threadIdx.x; e < 64 * VP; e += 128) {
+                const int r = e / VP, i = e % VP;
+                sv[r * LV + i] = (r < nk && i < b.vdim) ? vbase[(size_t)(j0 + r) * vld + i] : __float2bfloat16_rn(0.0f);
+            }
+        }
+        __syncthreads();
+        if (j0 > pos0 + warp * 16 + 15) continue;        // every key of the tile lies after this warp's rows
+        float sc[8][4];
+#pragma unroll
+        for (int n = 0; n < 8; n++) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f; }
+#pragma unroll
+        for (int kk = 0; kk < DP / 16; kk++) {
+            uint32_t a[4];
+            sa_ldsm_x4(sq_a + (uint32_t)(((warp * 16 + (lane & 15)) * LQ + kk * 16 + (lane >> 4) * 8) * 2), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int n2 = 0; n2 < 4; n2++) {
+                uint32_t b0, b1, b2, b3;
+                sa_ldsm_x4(sk_a + (uint32_t)(((n2 * 16 + (lane & 7) + (lane >> 4) * 8) * LQ + kk * 16 + ((lane >> 3) & 1) * 8) * 2), b0, b1, b2, b3);
+                sa_mma(sc[2 * n2], a, b0, b1);
+                sa_mma(sc[2 * n2 + 1], a, b2, b3);
+            }
+        }
+        // weights: rows gq and gq + 8 of the warp's 16, keys j0 + 8 n + 2 tq (+1)
+        const int p_lo = pos0 + warp * 16 + gq, p_hi = p_lo + 8;
+        uint32_t w[8][2];
+#pragma unroll
+        for (int n = 0; n < 8; n++) {
+            const int key = j0 + n * 8 + tq * 2;
+            const float w0 = key <= p_lo ? sigmoidf_(sc[n][0] * b.scale + bias) : 0.0f;
+            const float w1 = key + 1 <= p_lo ? sigmoidf_(sc[n][1] * b.scale + bias) : 0.0f;
+            const float w2 = key <= p_hi ? sigmoidf_(sc[n][2] * b.scale + bias) : 0.0f;
+            const float w3 = key + 1 <= p_hi ? sigmoidf_(sc[n][3] * b.scale + bias) : 0.0f;
+            w[n][0] = sa_pack(w0, w1);
+            w[n][1] = sa_pack(w2, w3);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) {                 // 16 keys per step
+            const uint32_t a[4] = {w[2 * kk][0], w[2 * kk][1], w[2 * kk + 1][0], w[2 * kk + 1][1]};
+#pragma unroll
+            for (int n2 = 0; n2 < VP / 16; n2++) {
+                uint32_t b0, b1, b2, b3;
+                sa_ldsm_x4_t(sv_a + (uint32_t)(((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LV + n2 * 16 + (lane >> 4) * 8) * 2), b0, b1, b2, b3);
+                sa_mma(o[2 * n2], a, b0, b1);
+                sa_mma(o[2 * n2 + 1], a, b2, b3);
+            }
+        }
+    }
+    const int r_lo = warp * 16 + gq, r_hi = r_lo + 8;
+#pragma unroll
+    for (int n = 0; n < VP / 8; n++) {
+        const int c = n * 8 + tq * 2;
+#pragma unroll
+        for (int x = 0; x < 2; x++) {
+            if (c + x >= b.vdim) continue;
+            if (r_lo < nq) out[(size_t)(row0 + r_lo) * ld_out + b.a_off + h * b.vdim + c + x] = __float2bfloat16_rn(o[n][x] * b.out_scale);
+            if (r_hi < nq) out[(size_t)(row0 + r_hi) * ld_out + b.a_off + h * b.vdim + c + x] = __float2bfloat16_rn(o[n][2 + x] * b.out_scale);
         }
     }
 }
