@@ -1,0 +1,210 @@
+"""`bench.py --workload reninex`: prefill and decode throughput of the Reninex family at layer sizes that resemble a real model
+(random weights), beside TinyLlama at the same layer shape and layer count.  Timed with CUDA events on each library's own stream,
+after warm-up; the weights of one pass (hundreds of MB) are larger than L2, so every pass streams them from HBM."""
+from __future__ import annotations
+
+import json
+import time
+
+import numpy as np
+
+SIZES = {
+    # name: width, ff, left (heads, kv, dim), right (heads, dim, vdim)
+    "w2048": dict(width=2048, ff=5632, l_heads=32, l_kv=4, l_dim=64, l_vdim=64, r_heads=16, r_dim=128, r_vdim=128, rot_dims=64),
+    "w1024": dict(width=1024, ff=2816, l_heads=16, l_kv=4, l_dim=64, l_vdim=64, r_heads=8, r_dim=128, r_vdim=128, rot_dims=64),
+}
+
+
+def _events(torch, stream, fn, iters, warmup):
+    with torch.cuda.stream(stream):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+        for a, b in ev:
+            a.record(stream)
+            fn()
+            b.record(stream)
+        torch.cuda.synchronize()
+    return float(np.median([a.elapsed_time(b) for a, b in ev]))
+
+
+def matmul_params(desc) -> int:
+    """Weights that every token multiplies (per pass over the layer runs), head included."""
+    W, n = desc["width"], 0
+    runs = run_count(desc)
+    for i, l in enumerate(desc["layers"]):
+        per = 0
+        for b in l["branches"]:
+            kvh = b.get("kv_heads", b["heads"])
+            per += W * (b["heads"] * b["dim"] + kvh * (b["dim"] + b["vdim"]) + (b["heads"] * b["vdim"] if b.get("gated") else 0) + b["heads"] * b["vdim"])
+        per += 3 * W * l["ff"]
+        n += per * runs[i]
+    lp = desc.get("loop")
+    if lp:
+        n += lp["times"] * 2 * W * W
+    return n + desc["vocab"] * W
+
+
+def run_count(desc):
+    lp = desc.get("loop")
+    return [lp["times"] if lp and lp["start"] <= i < lp["stop"] else 1 for i in range(len(desc["layers"]))]
+
+
+def mixer_flops(desc, T) -> float:
+    """Sigmoid attention (causal, T keys) and retention (state update + read) FLOPs of a T-token prompt."""
+    f, runs = 0.0, run_count(desc)
+    for i, l in enumerate(desc["layers"]):
+        for b in l["branches"]:
+            if b["kind"] == 1:
+                f += runs[i] * 2.0 * b["heads"] * (b["dim"] + b["vdim"]) * T * (T + 1) / 2
+            else:
+                f += runs[i] * 4.0 * b["heads"] * b["dim"] * b["vdim"] * T
+    return f
+
+
+def reninex_section(torch, name, layers, T, iters, warmup, peaks):
+    from . import reninex, seq
+    cfg = reninex.make_config(vocab=32000, n_layers=layers, taps=4, bigram=(65521, 31, 17), loop=None, **SIZES[name])
+    desc = reninex.describe(cfg)
+    t0 = time.time()
+    rng = np.random.default_rng(0)
+    tensors = {}
+    for k, shape in reninex.tensor_shapes(desc).items():          # cheap random bf16 patterns of the right scale
+        n = int(np.prod(shape)) if shape else 1
+        leaf = k.split(".")[-1]
+        if leaf in ("norm1", "norm"):
+            a = np.full(n, 0x3F80, np.uint16)
+        else:
+            std = 0.3 if leaf.startswith("canon") else (1.0 if k in ("embed", "bigram") else 1.0 / np.sqrt(shape[-1]))
+            a = reninex.st.f32_to_bf16_bits((rng.standard_normal(n, np.float32) * np.float32(std)))
+        tensors[k] = a.reshape(shape)
+    n_slots = 8
+    m = seq.SeqModel(desc, seq.BF16, n_slots, T + 64, max_rows=T).load(tensors)
+    stream = torch.cuda.ExternalStream(seq.stream_handle(), device=torch.device("cuda", 0))
+    prompt = rng.integers(0, 32000, T).astype(np.int32)
+    out = {"size": name, "layers": layers, "params_matmul": matmul_params(desc), "weight_bytes": m.weight_bytes(), "setup_s": round(time.time() - t0, 1)}
+
+    def prefill():
+        m.reset(0)
+        m.step([(0, prompt)], [T - 1])
+    l0 = seq.launch_count()
+    prefill()
+    out["prefill_launches"] = seq.launch_count() - l0
+    ms = _events(torch, stream, prefill, iters, warmup)
+    flops = 2.0 * T * matmul_params(desc) - 2.0 * (T - 1) * desc["vocab"] * desc["width"] + mixer_flops(desc, T)
+    out["prefill"] = {"T": T, "ms": ms, "tokens_per_s": T / ms * 1e3, "tflops": flops / ms * 1e-9, "frac_of_bf16_peak": flops / ms * 1e-9 / peaks["tflops"],
+                      "note": "includes the host->device copy of the prompt and the device->host copy of the last row's logits"}
+    # decode at context T: 1 and 8 sequences, device-side greedy loop (CUDA-graph replay per step)
+    for s in range(n_slots):
+        m.reset(s)
+    m.step_greedy([(s, prompt[: T - 40]) for s in range(1)])
+    for s in range(1, n_slots):
+        m.step_greedy([(s, prompt[: T - 40])])
+    state_bytes = m.state_bytes_per_slot() * (T - 40) / (T + 64)
+    for nseq in (1, 8):
+        slots = list(range(nseq))
+        steps = 8
+
+        def dec():
+            for s in slots:
+                pass
+            m.decode(slots, steps)
+        # positions advance: rewind by re-prefilling is too slow, so time short bursts that stay inside max_ctx
+        m.decode(slots, 2)
+        t_ms = []
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                dec()
+                b.record(stream)
+                torch.cuda.synchronize()
+                t_ms.append(a.elapsed_time(b) / steps)
+        ms = float(np.median(t_ms))
+        by = m.weight_bytes() - 2 * desc["vocab"] * desc["width"] - (2 * 65522 * desc["width"]) + nseq * state_bytes
+        out[f"decode_{nseq}"] = {"ms_per_step": ms, "tokens_per_s": nseq / ms * 1e3, "bytes_per_step": by, "gbs": by / ms * 1e-6,
+                                 "frac_of_hbm_peak": by / ms * 1e-6 / peaks["hbm_gbs"]}
+    m.close()
+    return out
+
+
+def tinyllama_section(torch, layers, T, iters, warmup, peaks):
+    """The closest existing model at the same layer shape (width 2048, ff 5632) and layer count: FP16 weights."""
+    from . import capi, weights as W
+    capi.init(0)
+    cfg = W.mini_config(n_layers=layers, n_vocab=32000)
+    stream = torch.cuda.ExternalStream(capi.stream_handle(), device=torch.device("cuda", 0))
+    out = {"layers": layers}
+    for wname, wdt in (("fp16", W.F16), ("q8", W.Q8)):
+        eng = capi.Engine(cfg, T + 64, wdt).load(W.synth_weights(cfg, wdt, seed=1))
+        prompt = W.synth_prompt(7, T, cfg.n_vocab)
+        per_layer = 2 * cfg.n_embd * cfg.n_embd + 2 * cfg.kv_dim * cfg.n_embd + 3 * cfg.n_ffn * cfg.n_embd
+        flops = 2.0 * T * layers * per_layer + 2.0 * cfg.n_vocab * cfg.n_embd + layers * 2.0 * cfg.n_heads * 2 * cfg.d_head * T * (T + 1) / 2
+        ms = _events(torch, stream, lambda: eng.prefill_fast(prompt), iters, warmup)
+        out[f"prefill_{wname}"] = {"T": T, "ms": ms, "tokens_per_s": T / ms * 1e3, "tflops": flops / ms * 1e-9,
+                                   "frac_of_bf16_peak": flops / ms * 1e-9 / peaks["tflops"], "path": "gtb_engine_prefill_fast (tcgen05 GEMMs, mma.sync attention)"}
+        eng.prefill_fast(prompt[: T - 40])
+        steps = 8
+        t_ms = []
+        with torch.cuda.stream(stream):
+            eng.decode(2)
+            for _ in range(3):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                eng.decode(steps)
+                b.record(stream)
+                torch.cuda.synchronize()
+                t_ms.append(a.elapsed_time(b) / steps)
+        ms = float(np.median(t_ms))
+        by = cfg.decode_bytes(wdt, T - 30)
+        out[f"decode_{wname}"] = {"ms_per_step": ms, "tokens_per_s": 1e3 / ms, "bytes_per_step": by, "gbs": by / ms * 1e-6,
+                                  "frac_of_hbm_peak": by / ms * 1e-6 / peaks["hbm_gbs"], "path": "persistent exact kernel" if eng.uses_megakernel() else "one kernel per phase"}
+        if wdt == W.Q8:
+            eng.set_option("fast_decode", 1)
+            t_ms = []
+            with torch.cuda.stream(stream):
+                eng.decode(2)
+                for _ in range(3):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    eng.decode(steps)
+                    b.record(stream)
+                    torch.cuda.synchronize()
+                    t_ms.append(a.elapsed_time(b) / steps)
+            ms = float(np.median(t_ms))
+            out["decode_q8_order_free"] = {"ms_per_step": ms, "tokens_per_s": 1e3 / ms, "gbs": by / ms * 1e-6, "frac_of_hbm_peak": by / ms * 1e-6 / peaks["hbm_gbs"]}
+        eng.close()
+    return out
+
+
+def run(args, root, clock_sampler) -> None:
+    import torch
+    from . import build
+    build.build(target="seq")
+    torch.cuda.set_device(0)
+    p = root / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        peaks = {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d.get("bf16_tflops", 1590.0)), "source": "measured (MEASURED_PEAKS.json)"}
+    else:
+        peaks = {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
+    from . import seq
+    seq.init(0)
+    layers, T = 4, 2048
+    iters = max(3, min(args.steps if args.steps != 512 else 5, 20))
+    res = {"reninex": [], "peaks": peaks}
+    with clock_sampler(0) as clk:
+        for name in SIZES:
+            res["reninex"].append(reninex_section(torch, name, layers, T, iters, max(args.warmup if args.warmup != 16 else 3, 3), peaks))
+        try:
+            res["tinyllama_same_shape"] = tinyllama_section(torch, layers, T, iters, 3, peaks)
+        except Exception as e:            # the TinyLlama library is a separate build target
+            res["tinyllama_same_shape"] = {"unavailable": f"{type(e).__name__}: {e}"}
+    head = res["reninex"][0]
+    print(json.dumps({"metric": "reninex_prefill_tokens_per_s", "value": head["prefill"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "steps": iters, "warmup": 3, "ms_per_step": head["prefill"]["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16 operands, fp32 accumulation; fp32 stream, scores, state", "data": "synthetic",
+                      "config": {"workload": f"Reninex {head['size']} x {layers} layers, random weights: prefill of {T} tokens; decode at that context",
+                                 "l2": "weights of a pass exceed L2"},
+                      "detail": res, "gpu_launches": head["prefill_launches"], "clocks": clk.summary()}), flush=True)

@@ -26,6 +26,7 @@ using namespace gtb::seq;
 namespace {
 
 inline int pad64(int k) { return (k + 63) / 64 * 64; }
+constexpr int SPLIT_MAX_ROWS = 64;          // passes of at most this many rows may split a row's keys over several CTAs
 
 struct TensorDest {
     int kind = 0;              // 0: bf16 matrix block, 1: fp32 vector (converted)
@@ -83,6 +84,8 @@ struct gtb_seq_model {
     int max_rows = 0, n1_max = 0, ff_max = 0, kout_p_max = 0, ro_max = 0;
     float *x = nullptr, *x0 = nullptr, *h = nullptr, *P = nullptr, *G = nullptr, *O = nullptr, *logits = nullptr;
     void *opA = nullptr, *opB = nullptr, *opC = nullptr, *opL = nullptr, *opH = nullptr;
+    float* attn_part = nullptr;                  // split decode attention: partial sums [splits][SPLIT_MAX_ROWS][heads * vdim]
+    int attn_splits = 1;
     float* retU = nullptr;                       // chunked retention: per-chunk contributions / states [chunks][heads][dim][vdim]
     size_t retU_floats = 0;
     float* cap = nullptr;                        // [runs][max_rows][width]
@@ -143,10 +146,10 @@ int product(gtb_seq_model* m, const void* A, int lda, const bf16* W, int ldw, fl
         if (rc != -1) return rc;                 // -1: shape not supported by that kernel
     }
     if (M <= 8) {
-        dim3 grid((N + 7) / 8);
-        if (M <= 2) k_gemv_rows<OT, 2><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
-        else if (M <= 4) k_gemv_rows<OT, 4><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
-        else k_gemv_rows<OT, 8><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        if (M <= 1) k_gemv_rows<OT, 1, 2><<<(N + 15) / 16, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        else if (M <= 2) k_gemv_rows<OT, 2, 2><<<(N + 15) / 16, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        else if (M <= 4) k_gemv_rows<OT, 4, 4><<<(N + 31) / 32, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        else k_gemv_rows<OT, 8, 4><<<(N + 31) / 32, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
     } else {
         dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
         k_gemm_simt<OT><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
@@ -176,8 +179,9 @@ RetChunk ret_chunk(const gtb_seq_branch& d) {
     RetChunk r;
     r.C = d.dim <= 128 ? 64 : 32;
     r.vs = std::min(d.vdim, 64);
-    r.smem_kv = ((size_t)r.C * (d.dim + 1) + (size_t)r.C * r.vs) * sizeof(float);
-    r.smem_out = (2 * (size_t)r.C * (d.dim + 1) + (size_t)r.C * r.vs + (size_t)r.C * (r.C + 1) + (size_t)d.dim * r.vs) * sizeof(float);
+    const size_t dp = (d.dim + 3) & ~3, vsp = (r.vs + 3) & ~3;
+    r.smem_kv = ((size_t)r.C * dp + (size_t)r.C * vsp) * sizeof(float);
+    r.smem_out = (2 * (size_t)r.C * d.dim + (size_t)r.C * vsp + (size_t)r.C * r.C + (size_t)d.dim * vsp) * sizeof(float);
     r.ok = r.smem_out <= 200 * 1024;
     return r;
 }
@@ -237,10 +241,10 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
         GTB_LAUNCHED();
         OT* ob = l.ff > 0 ? opB : nullptr;
         if (c.taps > 0) {
-            k_canon<OT><<<R, 256, 0, st>>>(t, m->h, W, c.taps, l.canon_a, l.ff > 0 ? l.canon_b : nullptr, run.tail, opA, ob, wp);
+            k_canon<OT><<<dim3(R, (W + 255) / 256), 256, 0, st>>>(t, m->h, W, c.taps, l.canon_a, l.ff > 0 ? l.canon_b : nullptr, run.tail, opA, ob, wp);
             GTB_LAUNCHED();
             if (c.taps > 1) {
-                k_canon_tail<<<S, 256, 0, st>>>(t, m->h, W, c.taps, run.tail);
+                k_canon_tail<<<dim3(S, (W + 255) / 256), 256, 0, st>>>(t, m->h, W, c.taps, run.tail);
                 GTB_LAUNCHED();
             }
         } else {
@@ -266,12 +270,19 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
             const BranchW& b = l.br[bi];
             if (b.d.kind == GTB_MIX_SIGMOID_ATTN) {
                 const AttnBranch a = attn_args(m, b);
-                k_attn_prep<OT><<<R, 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[bi], (OT*)run.vc[bi]);
+                k_attn_prep<OT><<<dim3(R, (a.heads + 2 * a.kv_heads + 3) / 4), 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[bi], (OT*)run.vc[bi]);
                 GTB_LAUNCHED();
                 int done = -1;
                 if (portions && sizeof(OT) == 2 && a.dim <= 128 && a.vdim <= 128)
                     done = sigattn_mma(t, a, S, n_qtiles, m->P, l.n1, (const bf16*)run.kc[bi], (const bf16*)run.vc[bi], (bf16*)opC, l.kout_p);
                 if (done > 0) return done;
+                if (done < 0 && !portions && m->attn_splits > 1 && R <= SPLIT_MAX_ROWS) {
+                    k_sigattn_split<OT><<<dim3(R, a.heads, m->attn_splits), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], m->attn_part, R);
+                    GTB_LAUNCHED();
+                    k_sigattn_join<OT><<<R, 256, 0, st>>>(a, m->attn_part, R, m->attn_splits, opC, l.kout_p);
+                    GTB_LAUNCHED();
+                    done = 0;
+                }
                 if (done < 0) {
                     k_sigattn<OT><<<dim3(R, a.heads), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], opC, l.kout_p);
                     GTB_LAUNCHED();
@@ -290,12 +301,12 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                     if (rcfg.smem_kv > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_ret_chunk_kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rcfg.smem_kv));
                     k_ret_chunk_kv<<<dim3(n_chunks, a.heads, nvs), 256, rcfg.smem_kv, st>>>(t, a, m->P, l.n1, S, rcfg.C, rcfg.vs, m->retU);
                     GTB_LAUNCHED();
-                    k_ret_scan<<<dim3(S, a.heads), 256, 0, st>>>(t, a, S, rcfg.C, m->retU, run.state[bi]);
+                    k_ret_scan<<<dim3(S, a.heads, (a.dim * a.vdim + 255) / 256), 256, 0, st>>>(t, a, S, rcfg.C, m->retU, run.state[bi]);
                     GTB_LAUNCHED();
                     if (rcfg.smem_out > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_ret_chunk_out, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rcfg.smem_out));
                     k_ret_chunk_out<<<dim3(n_chunks, a.heads, nvs), 256, rcfg.smem_out, st>>>(t, a, m->P, l.n1, S, rcfg.C, rcfg.vs, m->retU, m->O);
                     GTB_LAUNCHED();
-                    k_ret_post<OT><<<R, 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
+                    k_ret_post<OT><<<dim3(R, (a.heads + 3) / 4), 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
                     GTB_LAUNCHED();
                     continue;
                 }
@@ -303,7 +314,7 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                 if (rl.smem > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_retention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rl.smem));
                 k_retention<<<dim3(S, a.heads), rl.block, rl.smem, st>>>(t, a, m->P, l.n1, run.state[bi], m->O);
                 GTB_LAUNCHED();
-                k_ret_post<OT><<<R, 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
+                k_ret_post<OT><<<dim3(R, (a.heads + 3) / 4), 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
                 GTB_LAUNCHED();
             }
         }
@@ -507,6 +518,14 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 m->retU_floats = std::max(m->retU_floats, chunks * d.heads * d.dim * d.vdim);
             }
     if (m->retU_floats) TRY(dalloc_t(m, &m->retU, m->retU_floats));
+    {   // key splits of decode-time attention: one CTA per ~256 keys of a full slot, at most 32
+        int hv = 0;
+        for (const LayerW& l : m->L)
+            for (int bi = 0; bi < l.d.n_branches; bi++)
+                if (l.br[bi].d.kind == GTB_MIX_SIGMOID_ATTN) hv = std::max(hv, l.br[bi].d.heads * l.br[bi].d.vdim);
+        m->attn_splits = std::max(1, std::min(32, c.max_ctx / 256));
+        if (hv > 0 && m->attn_splits > 1) TRY(dalloc_t(m, &m->attn_part, (size_t)m->attn_splits * SPLIT_MAX_ROWS * hv));
+    }
     TRY(dalloc_t(m, &m->logits, R * c.vocab));
     TRY(dalloc(m, &m->opA, R * wp * es));
     TRY(dalloc(m, &m->opB, R * wp * es));

@@ -59,9 +59,12 @@ __device__ __forceinline__ bool sq_wait(uint32_t bar, uint32_t parity, volatile 
     return false;
 }
 
+// tanh on the special-function unit: relative error ~2^-11, below the bf16 rounding of the value that is stored
 __device__ __forceinline__ float sq_gelu(float z) {
     const float c = 0.7978845608028654f;
-    return 0.5f * z * (1.0f + tanhf(c * (z + 0.044715f * z * z * z)));
+    float th;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(c * (z + 0.044715f * z * z * z)));
+    return 0.5f * z * (1.0f + th);
 }
 
 template <int BN, int EPI>
@@ -274,7 +277,9 @@ static int run(SeqGemmPlan* p, int epi, const void* A, int lda, const void* W, i
     if (!p || K <= 0 || (K % SQ_BK) || (lda % 8) || (ldw % 8) || (((uintptr_t)A | (uintptr_t)W) & 15)) return -1;
     // 256-wide tiles when they still give every SM a tile; otherwise 128-wide
     const int mt = (M + SQ_BM - 1) / SQ_BM;
-    const int bn = (mt * ((N + 255) / 256) >= ctx().sm_count) ? 256 : 128;
+    // (the 128-wide MMA reads as much of A from shared memory per FLOP as the 256-wide one reads of A and W together: it runs at about
+    // half the rate, so it only pays when 256-wide tiles would leave most SMs idle)
+    const int bn = (N > 128 && mt * ((N + 255) / 256) * 2 >= ctx().sm_count) ? 256 : 128;
     CUtensorMap ta, tb;
     int rc = make_map(p, &ta, A, M, K, lda, SQ_BM);
     if (rc) return rc;

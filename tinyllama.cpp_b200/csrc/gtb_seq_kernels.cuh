@@ -132,7 +132,7 @@ __global__ void k_canon(PassTables t, const float* __restrict__ h, int width, in
     const int r = blockIdx.x;
     const int s = t.row_seg[r], row0 = t.seg_row0[s], slot = t.seg_slot[s];
     const float* tl = tail + (size_t)slot * (taps - 1) * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
         float a = 0.0f, b = 0.0f;
         for (int j = 0; j < taps; j++) {
             const int src = r - (taps - 1) + j;
@@ -162,7 +162,7 @@ __global__ void k_canon_tail(PassTables t, const float* __restrict__ h, int widt
     const int row0 = t.seg_row0[s], len = t.seg_len[s], slot = t.seg_slot[s];
     if (t.slots[slot].stopped) return;
     float* tl = tail + (size_t)slot * (taps - 1) * width;
-    for (int c = threadIdx.x; c < width; c += blockDim.x)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x)
         for (int k = 0; k < taps - 1; k++) {
             const int off = len - (taps - 1) + k;          // offset inside the segment of the row that lands in entry k
             tl[(size_t)k * width + c] = (off >= 0) ? h[(size_t)(row0 + off) * width + c] : tl[(size_t)(k + len) * width + c];
@@ -218,40 +218,63 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const AT* __restrict__ A, int
     }
 }
 
-// Few rows (decode): one warp per output column streams its weight row once for all M <= 8 rows; lanes split K.
-template <typename AT, int MR>
+// Few rows (decode): the weight matrix is streamed exactly once for all M <= MR rows.  A warp owns NC output columns; the rows of A
+// are staged in shared memory (fp32) in chunks of GV_KC elements; a lane takes 8 consecutive k per step (one 16-byte weight load per
+// column, all NC of them issued before the first use) and the lanes' partial sums meet in a shuffle reduction.
+constexpr int GV_KC = 1024;
+template <typename AT, int MR, int NC>
 __global__ void __launch_bounds__(256) k_gemv_rows(const AT* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, float* __restrict__ C, int ldc,
                                                    int M, int N, int K, const float* __restrict__ bias, int accumulate) {
-    const int n = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-    if (n >= N) return;
-    float acc[MR];
+    __shared__ __align__(16) float sA[MR][GV_KC];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n0 = (blockIdx.x * 8 + warp) * NC;
+    float acc[MR][NC];
 #pragma unroll
-    for (int m = 0; m < MR; m++) acc[m] = 0.0f;
-    const bf16* w = W + (size_t)n * ldw;
-    for (int k = lane * 8; k < K; k += 256) {              // K % 64 == 0 and the rows are 16-byte aligned: 8 bf16 per load
-        const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
-        const bf16* wp = reinterpret_cast<const bf16*>(&wv);
-        float wf[8];
+    for (int m = 0; m < MR; m++)
 #pragma unroll
-        for (int i = 0; i < 8; i++) wf[i] = __bfloat162float(wp[i]);
+        for (int c = 0; c < NC; c++) acc[m][c] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += GV_KC) {
+        __syncthreads();
+        for (int e = threadIdx.x; e < MR * GV_KC; e += 256) {
+            const int m = e / GV_KC, kk = e % GV_KC;
+            sA[m][kk] = (m < M && k0 + kk < K) ? ldf<AT>(A + (size_t)m * lda + k0 + kk) : 0.0f;
+        }
+        __syncthreads();
+        const int kend = min(GV_KC, K - k0);
+#pragma unroll 2
+        for (int kk = lane * 8; kk < kend; kk += 256) {          // K % 64 == 0 and rows are 16-byte aligned
+            uint4 wv[NC];
 #pragma unroll
-        for (int m = 0; m < MR; m++)
-            if (m < M) {
-                const AT* a = A + (size_t)m * lda + k;
+            for (int c = 0; c < NC; c++)
+                wv[c] = (n0 + c < N) ? __ldg(reinterpret_cast<const uint4*>(W + (size_t)(n0 + c) * ldw + k0 + kk)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-                for (int i = 0; i < 8; i++) acc[m] = fmaf(ldf<AT>(a + i), wf[i], acc[m]);
+            for (int m = 0; m < MR; m++) {
+                const float4 a0 = *reinterpret_cast<const float4*>(&sA[m][kk]), a1 = *reinterpret_cast<const float4*>(&sA[m][kk + 4]);
+                const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                for (int c = 0; c < NC; c++) {
+                    const uint32_t ww[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++) {
+                        acc[m][c] = fmaf(av[2 * i], __uint_as_float(ww[i] << 16), acc[m][c]);
+                        acc[m][c] = fmaf(av[2 * i + 1], __uint_as_float(ww[i] & 0xffff0000u), acc[m][c]);
+                    }
+                }
             }
-    }
-#pragma unroll
-    for (int m = 0; m < MR; m++) {
-        if (m >= M) break;
-        float v = warp_sum(acc[m]);
-        if (lane == 0) {
-            if (bias) v += bias[n];
-            if (accumulate) v += C[(size_t)m * ldc + n];
-            C[(size_t)m * ldc + n] = v;
         }
     }
+#pragma unroll
+    for (int m = 0; m < MR; m++)
+#pragma unroll
+        for (int c = 0; c < NC; c++) {
+            const float v = warp_sum(acc[m][c]);
+            if (lane == 0 && m < M && n0 + c < N) {
+                float o = v;
+                if (bias) o += bias[n0 + c];
+                if (accumulate) o += C[(size_t)m * ldc + n0 + c];
+                C[(size_t)m * ldc + n0 + c] = o;
+            }
+        }
 }
 
 // ------------------------------------------------------------------------------------------------ sigmoid attention
@@ -271,7 +294,7 @@ __global__ void k_attn_prep(PassTables t, AttnBranch b, float* __restrict__ P, i
     const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
     float* p = P + (size_t)r * ldp;
     const size_t crow = (size_t)slot * b.max_ctx + pos;
-    for (int u = wid; u < b.heads + 2 * b.kv_heads; u += nw) {
+    for (int u = blockIdx.y * nw + wid; u < b.heads + 2 * b.kv_heads; u += gridDim.y * nw) {
         if (u < b.heads + b.kv_heads) {
             const bool is_q = u < b.heads;
             float* v = p + (is_q ? b.q_off + u * b.dim : b.k_off + (u - b.heads) * b.dim);
@@ -341,6 +364,67 @@ __global__ void __launch_bounds__(128) k_sigattn(PassTables t, AttnBranch b, con
     for (int cc = 0; cc < 4; cc++) {
         const int c = threadIdx.x + cc * blockDim.x;
         if (c < b.vdim) out[(size_t)r * ld_out + b.a_off + h * b.vdim + c] = cvt<OT>(acc[cc] * b.out_scale);
+    }
+}
+
+// Decode rows at long contexts: the keys of a (row, head) are split over gridDim.z CTAs; each writes its partial sum to
+// part [split][R][heads * vdim] (zeros for an empty range), k_sigattn_join adds the splits in order.  Nothing is normalised over keys,
+// so the partial sums simply add.
+template <typename OT>
+__global__ void __launch_bounds__(128) k_sigattn_split(PassTables t, AttnBranch b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc,
+                                                       const OT* __restrict__ vc, float* __restrict__ part, int R) {
+    extern __shared__ float sm[];
+    float* sq = sm;
+    float* swt = sm + b.dim;
+    const int r = blockIdx.x, h = blockIdx.y, g = h / (b.heads / b.kv_heads);
+    const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
+    const int per = ((pos + 1 + (int)gridDim.z - 1) / (int)gridDim.z + 127) / 128 * 128;
+    const int lo = blockIdx.z * per, hi = min(pos + 1, lo + per);
+    const float* q = P + (size_t)r * ldp + b.q_off + h * b.dim;
+    for (int i = threadIdx.x; i < b.dim; i += blockDim.x) sq[i] = q[i];
+    const float bias = b.pb ? b.pb[h] : 0.0f;
+    const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
+    const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
+    const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    __syncthreads();
+    for (int j0 = lo; j0 < hi; j0 += blockDim.x) {
+        const int j = j0 + threadIdx.x;
+        float w = 0.0f;
+        if (j < hi) {
+            const OT* kr = kbase + (size_t)j * kld;
+            float s = 0.0f;
+            for (int i = 0; i < b.dim; i++) s = fmaf(sq[i], ldf<OT>(kr + i), s);
+            w = sigmoidf_(s * b.scale + bias);
+        }
+        swt[threadIdx.x] = w;
+        __syncthreads();
+        const int nj = min((int)blockDim.x, hi - j0);
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) {
+            const int c = threadIdx.x + cc * blockDim.x;
+            if (c < b.vdim) {
+                float a = acc[cc];
+                const OT* vr = vbase + (size_t)j0 * vld + c;
+                for (int jj = 0; jj < nj; jj++) a = fmaf(swt[jj], ldf<OT>(vr + (size_t)jj * vld), a);
+                acc[cc] = a;
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+        const int c = threadIdx.x + cc * blockDim.x;
+        if (c < b.vdim) part[((size_t)blockIdx.z * R + r) * (b.heads * b.vdim) + h * b.vdim + c] = acc[cc];
+    }
+}
+template <typename OT>
+__global__ void k_sigattn_join(AttnBranch b, const float* __restrict__ part, int R, int splits, OT* __restrict__ out, int ld_out) {
+    const int r = blockIdx.x, n = b.heads * b.vdim;
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        float a = 0.0f;
+        for (int k = 0; k < splits; k++) a += part[((size_t)k * R + r) * n + c];
+        out[(size_t)r * ld_out + b.a_off + c] = cvt<OT>(a * b.out_scale);
     }
 }
 
@@ -420,7 +504,7 @@ __global__ void k_retention(PassTables t, RetBranch b, const float* __restrict__
 template <typename OT>
 __global__ void k_ret_post(RetBranch b, const float* __restrict__ O, const float* __restrict__ P, int ldp, OT* __restrict__ out, int ld_out) {
     const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
-    for (int h = wid; h < b.heads; h += nw) {
+    for (int h = blockIdx.y * nw + wid; h < b.heads; h += gridDim.y * nw) {
         const float* o = O + (size_t)r * (b.heads * b.vdim) + h * b.vdim;
         float sc = b.out_scale;
         if (b.out_norm) {
@@ -538,35 +622,37 @@ __global__ void k_ret_rotate(PassTables t, RetBranch b, float* __restrict__ P, i
     }
 }
 
-// grid (chunks, heads, value slices); U [chunk][head][dim][vdim]
+// grid (chunks, heads, value slices); U [chunk][head][dim][vdim].  Shared memory: k' [C][dp] (k times g^(L-1-b)), v [C][vsp]; a thread
+// accumulates 4 x 4 tiles of U from float4 reads (dp, vsp: dim and the slice width rounded up to 4, zero-filled).
 __global__ void __launch_bounds__(256) k_ret_chunk_kv(PassTables t, RetBranch b, const float* __restrict__ P, int ldp, int S, int C, int vs,
                                                       float* __restrict__ U) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     int seg, c;
     if (!ret_find_chunk(t, S, C, blockIdx.x, seg, c)) return;
     const int h = blockIdx.y, j0 = blockIdx.z * vs, nv = min(vs, b.vdim - j0);
     const int row0 = t.seg_row0[seg] + c * C, L = min(C, t.seg_len[seg] - c * C);
-    float* sk = sm;                       // [C][dim + 1], already times g^(L-1-b)
-    float* sv = sm + C * (b.dim + 1);     // [C][vs]
+    const int dp = (b.dim + 3) & ~3, vsp = (vs + 3) & ~3;
+    float* sk = sm;                 // [C][dp]
+    float* sv = sm + C * dp;        // [C][vsp]
     const float lg = logf(b.decay[h]);
-    for (int e = threadIdx.x; e < L * b.dim; e += blockDim.x) {
-        const int bb = e / b.dim, i = e % b.dim;
-        sk[bb * (b.dim + 1) + i] = P[(size_t)(row0 + bb) * ldp + b.k_off + h * b.dim + i] * expf(lg * (float)(L - 1 - bb));
+    for (int e = threadIdx.x; e < C * dp; e += blockDim.x) {
+        const int bb = e / dp, i = e % dp;
+        sk[e] = (bb < L && i < b.dim) ? P[(size_t)(row0 + bb) * ldp + b.k_off + h * b.dim + i] * expf(lg * (float)(L - 1 - bb)) : 0.0f;
     }
-    for (int e = threadIdx.x; e < L * nv; e += blockDim.x) {
-        const int bb = e / nv, j = e % nv;
-        sv[bb * vs + j] = P[(size_t)(row0 + bb) * ldp + b.v_off + h * b.vdim + j0 + j];
+    for (int e = threadIdx.x; e < C * vsp; e += blockDim.x) {
+        const int bb = e / vsp, j = e % vsp;
+        sv[e] = (bb < L && j < nv) ? P[(size_t)(row0 + bb) * ldp + b.v_off + h * b.vdim + j0 + j] : 0.0f;
     }
     __syncthreads();
     float* u = U + (((size_t)blockIdx.x * b.heads + h) * b.dim) * b.vdim;
-    const int tj = (nv + 3) / 4, ti = (b.dim + 3) / 4;
+    const int tj = vsp / 4, ti = dp / 4;
     for (int tile = threadIdx.x; tile < ti * tj; tile += blockDim.x) {
         const int i4 = (tile / tj) * 4, j4 = (tile % tj) * 4;
         float acc[4][4] = {};
         for (int bb = 0; bb < L; bb++) {
-            float kk[4], vv[4];
-#pragma unroll
-            for (int x = 0; x < 4; x++) { kk[x] = (i4 + x < b.dim) ? sk[bb * (b.dim + 1) + i4 + x] : 0.0f; vv[x] = (j4 + x < nv) ? sv[bb * vs + j4 + x] : 0.0f; }
+            const float4 k4 = *reinterpret_cast<const float4*>(sk + bb * dp + i4);
+            const float4 v4 = *reinterpret_cast<const float4*>(sv + bb * vsp + j4);
+            const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
             for (int x = 0; x < 4; x++)
 #pragma unroll
@@ -580,90 +666,123 @@ __global__ void __launch_bounds__(256) k_ret_chunk_kv(PassTables t, RetBranch b,
     }
 }
 
-// grid (segments, heads): element-parallel scan over the segment's chunks
+// grid (segments, heads, blocks of state elements): every state element walks the segment's chunks on its own
 __global__ void __launch_bounds__(256) k_ret_scan(PassTables t, RetBranch b, int S, int C, float* __restrict__ U, float* __restrict__ state) {
     const int seg = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    if (e >= b.dim * b.vdim) return;
     int first = 0;
     for (int s = 0; s < seg; s++) first += (t.seg_len[s] + C - 1) / C;
     const int len = t.seg_len[seg], nchunk = (len + C - 1) / C, slot = t.seg_slot[seg];
     float* gs = state + ((size_t)slot * b.heads + h) * (size_t)b.dim * b.vdim;
     const float lg = logf(b.decay[h]);
-    const bool live = !t.slots[slot].stopped;
-    for (int e = threadIdx.x; e < b.dim * b.vdim; e += blockDim.x) {
-        float s0 = gs[e];
-        for (int c = 0; c < nchunk; c++) {
-            float* u = U + (((size_t)(first + c) * b.heads + h) * b.dim) * b.vdim + e;
-            const float add = *u;
-            *u = s0;
-            s0 = fmaf(expf(lg * (float)min(C, len - c * C)), s0, add);
-        }
-        if (live) gs[e] = s0;
+    const float gc = expf(lg * (float)C);
+    float s0 = gs[e];
+    float* u = U + (((size_t)first * b.heads + h) * b.dim) * b.vdim + e;
+    const size_t stride = (size_t)b.heads * b.dim * b.vdim;
+    for (int c = 0; c < nchunk; c++, u += stride) {
+        const float add = *u;
+        *u = s0;
+        const int Lc = min(C, len - c * C);
+        s0 = fmaf(Lc == C ? gc : expf(lg * (float)Lc), s0, add);
     }
+    if (!t.slots[slot].stopped) gs[e] = s0;
 }
 
-// grid (chunks, heads, value slices); Sb [chunk][head][dim][vdim] = state before the chunk; O [R][heads * vdim]
+// grid (chunks, heads, value slices); Sb [chunk][head][dim][vdim] = state before the chunk; O [R][heads * vdim].
+// Shared memory, all zero-filled beyond the chunk's rows and the slice's columns: qT, kT [dim][C] (position-minor, so that four rows
+// are one float4), v [C][vsp], aT [C keys][C rows] = g^(a-b) q_a.k_b for b <= a, s0 [dim][vsp].  Three products on 4 x 4 register tiles.
 __global__ void __launch_bounds__(256) k_ret_chunk_out(PassTables t, RetBranch b, const float* __restrict__ P, int ldp, int S, int C, int vs,
                                                        const float* __restrict__ Sb, float* __restrict__ O) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     int seg, c;
     if (!ret_find_chunk(t, S, C, blockIdx.x, seg, c)) return;
     const int h = blockIdx.y, j0 = blockIdx.z * vs, nv = min(vs, b.vdim - j0);
     const int row0 = t.seg_row0[seg] + c * C, L = min(C, t.seg_len[seg] - c * C);
-    const int ldq = b.dim + 1;
-    float* sq = sm;                       // [C][dim + 1]
-    float* sk = sq + C * ldq;             // [C][dim + 1]
-    float* sv = sk + C * ldq;             // [C][vs]
-    float* sa = sv + C * vs;              // [C][C + 1]
-    float* s0 = sa + C * (C + 1);         // [dim][vs]
+    const int vsp = (vs + 3) & ~3;
+    float* sq = sm;                       // [dim][C]
+    float* sk = sq + b.dim * C;           // [dim][C]
+    float* sv = sk + b.dim * C;           // [C][vsp]
+    float* sa = sv + C * vsp;             // [C][C]
+    float* s0 = sa + C * C;               // [dim][vsp]
     const float lg = logf(b.decay[h]);
-    for (int e = threadIdx.x; e < L * b.dim; e += blockDim.x) {
-        const int bb = e / b.dim, i = e % b.dim;
-        const float* p = P + (size_t)(row0 + bb) * ldp;
-        sq[bb * ldq + i] = p[b.q_off + h * b.dim + i];
-        sk[bb * ldq + i] = p[b.k_off + h * b.dim + i];
+    for (int e = threadIdx.x; e < C * b.dim; e += blockDim.x) {
+        const int bb = e % C, i = e / C;
+        float qv = 0.0f, kv = 0.0f;
+        if (bb < L) {
+            const float* p = P + (size_t)(row0 + bb) * ldp;
+            qv = p[b.q_off + h * b.dim + i];
+            kv = p[b.k_off + h * b.dim + i];
+        }
+        sq[e] = qv;
+        sk[e] = kv;
     }
-    for (int e = threadIdx.x; e < L * nv; e += blockDim.x) {
-        const int bb = e / nv, j = e % nv;
-        sv[bb * vs + j] = P[(size_t)(row0 + bb) * ldp + b.v_off + h * b.vdim + j0 + j];
+    for (int e = threadIdx.x; e < C * vsp; e += blockDim.x) {
+        const int bb = e / vsp, j = e % vsp;
+        sv[e] = (bb < L && j < nv) ? P[(size_t)(row0 + bb) * ldp + b.v_off + h * b.vdim + j0 + j] : 0.0f;
     }
     const float* sb = Sb + (((size_t)blockIdx.x * b.heads + h) * b.dim) * b.vdim;
-    for (int e = threadIdx.x; e < b.dim * nv; e += blockDim.x) {
-        const int i = e / nv, j = e % nv;
-        s0[i * vs + j] = sb[(size_t)i * b.vdim + j0 + j];
+    for (int e = threadIdx.x; e < b.dim * vsp; e += blockDim.x) {
+        const int i = e / vsp, j = e % vsp;
+        s0[e] = j < nv ? sb[(size_t)i * b.vdim + j0 + j] : 0.0f;
     }
     __syncthreads();
-    // A[a][bb] = g^(a - bb) q_a . k_bb for bb <= a
-    for (int e = threadIdx.x; e < L * L; e += blockDim.x) {
-        const int a = e / L, bb = e % L;
-        float d = 0.0f;
-        if (bb <= a) {
-            for (int i = 0; i < b.dim; i++) d = fmaf(sq[a * ldq + i], sk[bb * ldq + i], d);
-            d *= expf(lg * (float)(a - bb));
+    const int tc = C / 4;
+    for (int tile = threadIdx.x; tile < tc * tc; tile += blockDim.x) {
+        const int a4 = (tile / tc) * 4, b4 = (tile % tc) * 4;
+        float acc[4][4] = {};                           // [key][row]
+        if (b4 <= a4 + 3 && a4 < L) {
+            for (int i = 0; i < b.dim; i++) {
+                const float4 q4 = *reinterpret_cast<const float4*>(sq + i * C + a4);
+                const float4 k4 = *reinterpret_cast<const float4*>(sk + i * C + b4);
+                const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+                for (int y = 0; y < 4; y++)
+#pragma unroll
+                    for (int x = 0; x < 4; x++) acc[y][x] = fmaf(kk[y], qq[x], acc[y][x]);
+            }
         }
-        sa[a * (C + 1) + bb] = d;
+#pragma unroll
+        for (int y = 0; y < 4; y++)
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const int a = a4 + x, bb = b4 + y;
+                sa[bb * C + a] = (bb <= a) ? acc[y][x] * expf(lg * (float)(a - bb)) : 0.0f;
+            }
     }
     __syncthreads();
-    // o[a][j] = sum_bb A[a][bb] v[bb][j] + g^(a+1) sum_i q[a][i] S0[i][j]; a thread owns 4 consecutive rows of one value channel
-    const int ta = (L + 3) / 4;
-    for (int tile = threadIdx.x; tile < ta * nv; tile += blockDim.x) {
-        const int a4 = (tile / nv) * 4, j = tile % nv;
-        float intra[4] = {0, 0, 0, 0}, inter[4] = {0, 0, 0, 0};
+    const int tj = vsp / 4;
+    for (int tile = threadIdx.x; tile < tc * tj; tile += blockDim.x) {
+        const int a4 = (tile / tj) * 4, j4 = (tile % tj) * 4;
+        if (a4 >= L) continue;
+        float intra[4][4] = {}, inter[4][4] = {};       // [row][channel]
         const int bmax = min(L, a4 + 4);
         for (int bb = 0; bb < bmax; bb++) {
-            const float v = sv[bb * vs + j];
+            const float4 w4 = *reinterpret_cast<const float4*>(sa + bb * C + a4);
+            const float4 v4 = *reinterpret_cast<const float4*>(sv + bb * vsp + j4);
+            const float ww[4] = {w4.x, w4.y, w4.z, w4.w}, vv[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
             for (int x = 0; x < 4; x++)
-                if (a4 + x < L) intra[x] = fmaf(sa[(a4 + x) * (C + 1) + bb], v, intra[x]);
+#pragma unroll
+                for (int y = 0; y < 4; y++) intra[x][y] = fmaf(ww[x], vv[y], intra[x][y]);
         }
         for (int i = 0; i < b.dim; i++) {
-            const float s = s0[i * vs + j];
+            const float4 q4 = *reinterpret_cast<const float4*>(sq + i * C + a4);
+            const float4 z4 = *reinterpret_cast<const float4*>(s0 + i * vsp + j4);
+            const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, zz[4] = {z4.x, z4.y, z4.z, z4.w};
 #pragma unroll
             for (int x = 0; x < 4; x++)
-                if (a4 + x < L) inter[x] = fmaf(sq[(a4 + x) * ldq + i], s, inter[x]);
+#pragma unroll
+                for (int y = 0; y < 4; y++) inter[x][y] = fmaf(qq[x], zz[y], inter[x][y]);
         }
 #pragma unroll
-        for (int x = 0; x < 4; x++)
-            if (a4 + x < L) O[(size_t)(row0 + a4 + x) * (b.heads * b.vdim) + h * b.vdim + j0 + j] = fmaf(expf(lg * (float)(a4 + x + 1)), inter[x], intra[x]);
+        for (int x = 0; x < 4; x++) {
+            if (a4 + x >= L) continue;
+            const float ga = expf(lg * (float)(a4 + x + 1));
+#pragma unroll
+            for (int y = 0; y < 4; y++)
+                if (j4 + y < nv) O[(size_t)(row0 + a4 + x) * (b.heads * b.vdim) + h * b.vdim + j0 + j4 + y] = fmaf(ga, inter[x][y], intra[x][y]);
+        }
     }
 }
 

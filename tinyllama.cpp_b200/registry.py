@@ -12,6 +12,12 @@ def _open_reninex(path: Path, dtype: str, n_slots: int, max_ctx: int, max_rows: 
     from . import reninex, seq
     seq.init(device)
     desc, tensors = reninex.read_checkpoint(path)
+    known = reninex.tensor_shapes(desc)
+    extra = sorted(set(tensors) - set(known))
+    if extra:                                   # e.g. a filter of a feed-forward that the layer does not have
+        import sys
+        print(f"{path}: ignoring {len(extra)} tensors the description does not use: {', '.join(extra[:4])}{' ...' if len(extra) > 4 else ''}", file=sys.stderr)
+        tensors = {k: v for k, v in tensors.items() if k in known}
     if dtype not in seq.MODE_BY_NAME:
         raise ValueError(f"dtype {dtype!r}: this family runs in bfloat16 or float32")
     return seq.SeqModel(desc, seq.MODE_BY_NAME[dtype], n_slots, max_ctx, max_rows).load(tensors)
