@@ -99,6 +99,9 @@ int gtb_seq_last_logits(gtb_seq_t m, int seg, float* h_logits);
  * "fused_attn" (1, default: tensor-core prefill kernels for the mixers where shapes allow; 0: the simple kernels) */
 int gtb_seq_set_option(gtb_seq_t m, const char* name, int value);
 int gtb_seq_read_capture(gtb_seq_t m, int run, int row, float* h_out);    /* [width] */
+/* self-test and timing of the bf16 tensor-core product on host data: C [M][N] = A [M][K] . W [N][K]^T (+ the incoming C when accumulate);
+ * operands are placed with a row stride of K + ld_extra elements; *ms = mean device time of `iters` further runs */
+int gtb_seq_selftest_gemm(const void* h_A, const void* h_W, float* h_C, int M, int N, int K, int ld_extra, int accumulate, int iters, float* ms);
 int gtb_seq_weight_bytes(gtb_seq_t m, size_t* nbytes);
 int gtb_seq_state_bytes_per_slot(gtb_seq_t m, size_t* nbytes);
 

@@ -146,10 +146,10 @@ int product(gtb_seq_model* m, const void* A, int lda, const bf16* W, int ldw, fl
         if (rc != -1) return rc;                 // -1: shape not supported by that kernel
     }
     if (M <= 8) {
-        if (M <= 1) k_gemv_rows<OT, 1, 2><<<(N + 15) / 16, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
-        else if (M <= 2) k_gemv_rows<OT, 2, 2><<<(N + 15) / 16, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
-        else if (M <= 4) k_gemv_rows<OT, 4, 4><<<(N + 31) / 32, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
-        else k_gemv_rows<OT, 8, 4><<<(N + 31) / 32, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        if (M <= 1) k_gemv_rows<OT, 1, 4><<<(N + 3) / 4, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        else if (M <= 2) k_gemv_rows<OT, 2, 4><<<(N + 3) / 4, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        else if (M <= 4) k_gemv_rows<OT, 4, 4><<<(N + 3) / 4, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        else k_gemv_rows<OT, 8, 4><<<(N + 3) / 4, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
     } else {
         dim3 grid((N + SG_BN - 1) / SG_BN, (M + SG_BM - 1) / SG_BM);
         k_gemm_simt<OT><<<grid, 256, 0, st>>>(a, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
@@ -279,7 +279,7 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                 if (done < 0 && !portions && m->attn_splits > 1 && R <= SPLIT_MAX_ROWS) {
                     k_sigattn_split<OT><<<dim3(R, a.heads, m->attn_splits), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], m->attn_part, R);
                     GTB_LAUNCHED();
-                    k_sigattn_join<OT><<<R, 256, 0, st>>>(a, m->attn_part, R, m->attn_splits, opC, l.kout_p);
+                    k_sigattn_join<OT><<<dim3(R, (a.heads * a.vdim + 255) / 256), 256, 0, st>>>(a, m->attn_part, R, m->attn_splits, opC, l.kout_p);
                     GTB_LAUNCHED();
                     done = 0;
                 }
@@ -866,6 +866,40 @@ int gtb_seq_read_capture(gtb_seq_t m, int run, int row, float* h_out) {
     GTB_CUDA(cudaMemcpyAsync(h_out, m->cap + ((size_t)run * m->max_rows + row) * m->cfg.width, m->cfg.width * sizeof(float), cudaMemcpyDeviceToHost, ctx().stream));
     GTB_CUDA(cudaStreamSynchronize(ctx().stream));
     return GTB_OK;
+}
+
+// self-test / timing of the bf16 tensor-core product on host data: C = A . W^T (+ C0 when accumulate), ld = K + ld_extra elements
+int gtb_seq_selftest_gemm(const void* h_A, const void* h_W, float* h_C, int M, int N, int K, int ld_extra, int accumulate, int iters, float* ms) {
+    GTB_CHECK_INIT();
+    GTB_ARG(h_A && h_W && h_C && M > 0 && N > 0 && K > 0 && K % 64 == 0 && ld_extra >= 0 && ld_extra % 8 == 0 && iters >= 1);
+    SeqGemmPlan* gp = nullptr;
+    int rc = seq_gemm_create(&gp);
+    if (rc) return rc;
+    const int ld = K + ld_extra;
+    bf16 *dA = nullptr, *dW = nullptr;
+    float* dC = nullptr;
+    cudaEvent_t e0 = nullptr, e1 = nullptr;
+    cudaStream_t st = ctx().stream;
+    auto done = [&](int code) { cudaFree(dA); cudaFree(dW); cudaFree(dC); if (e0) cudaEventDestroy(e0); if (e1) cudaEventDestroy(e1); seq_gemm_destroy(gp); return code; };
+    if (cudaMalloc((void**)&dA, (size_t)M * ld * 2) != cudaSuccess || cudaMalloc((void**)&dW, (size_t)N * ld * 2) != cudaSuccess ||
+        cudaMalloc((void**)&dC, (size_t)M * N * 4) != cudaSuccess) return done(gtb::fail(GTB_ERR_CUDA, "cudaMalloc failed"));
+    cudaMemset(dA, 0, (size_t)M * ld * 2);
+    cudaMemset(dW, 0, (size_t)N * ld * 2);
+    cudaMemcpy2D(dA, (size_t)ld * 2, h_A, (size_t)K * 2, (size_t)K * 2, M, cudaMemcpyHostToDevice);
+    cudaMemcpy2D(dW, (size_t)ld * 2, h_W, (size_t)K * 2, (size_t)K * 2, N, cudaMemcpyHostToDevice);
+    cudaMemcpy(dC, h_C, (size_t)M * N * 4, cudaMemcpyHostToDevice);
+    rc = seq_gemm_bf16(gp, dA, ld, dW, ld, dC, N, M, N, K, nullptr, accumulate);
+    if (rc) return done(rc == -1 ? gtb::fail(GTB_ERR_ARG, "shape not supported by the tensor-core product") : rc);
+    cudaMemcpyAsync(h_C, dC, (size_t)M * N * 4, cudaMemcpyDeviceToHost, st);
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    cudaEventRecord(e0, st);
+    for (int i = 0; i < iters; i++) seq_gemm_bf16(gp, dA, ld, dW, ld, dC, N, M, N, K, nullptr, 0);
+    cudaEventRecord(e1, st);
+    if (cudaStreamSynchronize(st) != cudaSuccess) return done(gtb::fail(GTB_ERR_CUDA, "the product failed: %s", cudaGetErrorString(cudaGetLastError())));
+    if (ms) { cudaEventElapsedTime(ms, e0, e1); *ms /= iters; }
+    int bad = 0;
+    seq_gemm_status(gp, &bad);
+    return done(bad ? gtb::fail(GTB_ERR_STATE, "the product gave up on a pipeline wait") : GTB_OK);
 }
 
 int gtb_seq_weight_bytes(gtb_seq_t m, size_t* nbytes) { GTB_ARG(m && nbytes); *nbytes = m->weight_bytes; return GTB_OK; }

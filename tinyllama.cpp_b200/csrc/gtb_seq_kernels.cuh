@@ -66,6 +66,37 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 }
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+
+// dot of a shared-memory fp32 vector with a cached key row; `vec`: the row is 16-byte aligned and n a multiple of 8 (4 for fp32)
+__device__ __forceinline__ float key_dot(const float* __restrict__ q, const bf16* __restrict__ k, int n, bool vec) {
+    float s = 0.0f;
+    if (vec) {
+        for (int i = 0; i < n; i += 8) {
+            const uint4 v = *reinterpret_cast<const uint4*>(k + i);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                s = fmaf(q[i + 2 * j], __uint_as_float(w[j] << 16), s);
+                s = fmaf(q[i + 2 * j + 1], __uint_as_float(w[j] & 0xffff0000u), s);
+            }
+        }
+    } else {
+        for (int i = 0; i < n; i++) s = fmaf(q[i], __bfloat162float(k[i]), s);
+    }
+    return s;
+}
+__device__ __forceinline__ float key_dot(const float* __restrict__ q, const float* __restrict__ k, int n, bool vec) {
+    float s = 0.0f;
+    if (vec) {
+        for (int i = 0; i < n; i += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(k + i);
+            s = fmaf(q[i], v.x, s); s = fmaf(q[i + 1], v.y, s); s = fmaf(q[i + 2], v.z, s); s = fmaf(q[i + 3], v.w, s);
+        }
+    } else {
+        for (int i = 0; i < n; i++) s = fmaf(q[i], k[i], s);
+    }
+    return s;
+}
 __device__ __forceinline__ float gelu_tanh(float z) {
     const float c = 0.7978845608028654f;      // sqrt(2/pi)
     return 0.5f * z * (1.0f + tanhf(c * (z + 0.044715f * z * z * z)));
@@ -218,47 +249,50 @@ __global__ void __launch_bounds__(256) k_gemm_simt(const AT* __restrict__ A, int
     }
 }
 
-// Few rows (decode): the weight matrix is streamed exactly once for all M <= MR rows.  A warp owns NC output columns; the rows of A
-// are staged in shared memory (fp32) in chunks of GV_KC elements; a lane takes 8 consecutive k per step (one 16-byte weight load per
-// column, all NC of them issued before the first use) and the lanes' partial sums meet in a shuffle reduction.
-constexpr int GV_KC = 1024;
+// Few rows (decode): the weight matrix is streamed exactly once for all M <= MR rows.  A CTA owns NC output columns and its 8 warps
+// split K; a lane takes 8 consecutive k per step (one 16-byte weight load per column, all of them issued before the first use; the
+// rows of A come through L1 as 16-byte loads too), the lanes' partial sums meet in a shuffle reduction and the warps' in shared memory.
+template <typename AT> __device__ __forceinline__ void load8(const AT* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p + 4));
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<bf16>(const bf16* p, float (&v)[8]) {
+    const uint4 a = __ldg(reinterpret_cast<const uint4*>(p));
+    const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) { v[2 * i] = __uint_as_float(w[i] << 16); v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
 template <typename AT, int MR, int NC>
 __global__ void __launch_bounds__(256) k_gemv_rows(const AT* __restrict__ A, int lda, const bf16* __restrict__ W, int ldw, float* __restrict__ C, int ldc,
                                                    int M, int N, int K, const float* __restrict__ bias, int accumulate) {
-    __shared__ __align__(16) float sA[MR][GV_KC];
+    __shared__ float red[8][MR * NC];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n0 = (blockIdx.x * 8 + warp) * NC;
+    const int n0 = blockIdx.x * NC;
     float acc[MR][NC];
 #pragma unroll
     for (int m = 0; m < MR; m++)
 #pragma unroll
         for (int c = 0; c < NC; c++) acc[m][c] = 0.0f;
-    for (int k0 = 0; k0 < K; k0 += GV_KC) {
-        __syncthreads();
-        for (int e = threadIdx.x; e < MR * GV_KC; e += 256) {
-            const int m = e / GV_KC, kk = e % GV_KC;
-            sA[m][kk] = (m < M && k0 + kk < K) ? ldf<AT>(A + (size_t)m * lda + k0 + kk) : 0.0f;
-        }
-        __syncthreads();
-        const int kend = min(GV_KC, K - k0);
+    // K % 64 == 0 and every row is 16-byte aligned: steps of 8 elements never straddle the end
 #pragma unroll 2
-        for (int kk = lane * 8; kk < kend; kk += 256) {          // K % 64 == 0 and rows are 16-byte aligned
-            uint4 wv[NC];
+    for (int k = (warp * 32 + lane) * 8; k < K; k += 2048) {
+        uint4 wv[NC];
 #pragma unroll
-            for (int c = 0; c < NC; c++)
-                wv[c] = (n0 + c < N) ? __ldg(reinterpret_cast<const uint4*>(W + (size_t)(n0 + c) * ldw + k0 + kk)) : make_uint4(0, 0, 0, 0);
+        for (int c = 0; c < NC; c++)
+            wv[c] = (n0 + c < N) ? __ldg(reinterpret_cast<const uint4*>(W + (size_t)(n0 + c) * ldw + k)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-            for (int m = 0; m < MR; m++) {
-                const float4 a0 = *reinterpret_cast<const float4*>(&sA[m][kk]), a1 = *reinterpret_cast<const float4*>(&sA[m][kk + 4]);
-                const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+        for (int m = 0; m < MR; m++) {
+            if (m >= M) break;
+            float av[8];
+            load8<AT>(A + (size_t)m * lda + k, av);
 #pragma unroll
-                for (int c = 0; c < NC; c++) {
-                    const uint32_t ww[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
+            for (int c = 0; c < NC; c++) {
+                const uint32_t ww[4] = {wv[c].x, wv[c].y, wv[c].z, wv[c].w};
 #pragma unroll
-                    for (int i = 0; i < 4; i++) {
-                        acc[m][c] = fmaf(av[2 * i], __uint_as_float(ww[i] << 16), acc[m][c]);
-                        acc[m][c] = fmaf(av[2 * i + 1], __uint_as_float(ww[i] & 0xffff0000u), acc[m][c]);
-                    }
+                for (int i = 0; i < 4; i++) {
+                    acc[m][c] = fmaf(av[2 * i], __uint_as_float(ww[i] << 16), acc[m][c]);
+                    acc[m][c] = fmaf(av[2 * i + 1], __uint_as_float(ww[i] & 0xffff0000u), acc[m][c]);
                 }
             }
         }
@@ -268,13 +302,20 @@ __global__ void __launch_bounds__(256) k_gemv_rows(const AT* __restrict__ A, int
 #pragma unroll
         for (int c = 0; c < NC; c++) {
             const float v = warp_sum(acc[m][c]);
-            if (lane == 0 && m < M && n0 + c < N) {
-                float o = v;
-                if (bias) o += bias[n0 + c];
-                if (accumulate) o += C[(size_t)m * ldc + n0 + c];
-                C[(size_t)m * ldc + n0 + c] = o;
-            }
+            if (lane == 0) red[warp][m * NC + c] = v;
         }
+    __syncthreads();
+    if (threadIdx.x < MR * NC) {
+        const int m = threadIdx.x / NC, c = threadIdx.x % NC;
+        if (m < M && n0 + c < N) {
+            float o = 0.0f;
+#pragma unroll
+            for (int w = 0; w < 8; w++) o += red[w][threadIdx.x];
+            if (bias) o += bias[n0 + c];
+            if (accumulate) o += C[(size_t)m * ldc + n0 + c];
+            C[(size_t)m * ldc + n0 + c] = o;
+        }
+    }
 }
 
 // ------------------------------------------------------------------------------------------------ sigmoid attention
@@ -335,15 +376,13 @@ __global__ void __launch_bounds__(128) k_sigattn(PassTables t, AttnBranch b, con
     const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
     const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const bool kvec = b.dim % 8 == 0;            // rows of the cache start on 16-byte boundaries then
     __syncthreads();
     for (int j0 = 0; j0 <= pos; j0 += blockDim.x) {
         const int j = j0 + threadIdx.x;
         float w = 0.0f;
         if (j <= pos) {
-            const OT* kr = kbase + (size_t)j * kld;
-            float s = 0.0f;
-            for (int i = 0; i < b.dim; i++) s = fmaf(sq[i], ldf<OT>(kr + i), s);
-            w = sigmoidf_(s * b.scale + bias);
+            w = sigmoidf_(key_dot(sq, kbase + (size_t)j * kld, b.dim, kvec) * b.scale + bias);
         }
         swt[threadIdx.x] = w;
         __syncthreads();
@@ -387,15 +426,13 @@ __global__ void __launch_bounds__(128) k_sigattn_split(PassTables t, AttnBranch 
     const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
     const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const bool kvec = b.dim % 8 == 0;            // rows of the cache start on 16-byte boundaries then
     __syncthreads();
     for (int j0 = lo; j0 < hi; j0 += blockDim.x) {
         const int j = j0 + threadIdx.x;
         float w = 0.0f;
         if (j < hi) {
-            const OT* kr = kbase + (size_t)j * kld;
-            float s = 0.0f;
-            for (int i = 0; i < b.dim; i++) s = fmaf(sq[i], ldf<OT>(kr + i), s);
-            w = sigmoidf_(s * b.scale + bias);
+            w = sigmoidf_(key_dot(sq, kbase + (size_t)j * kld, b.dim, kvec) * b.scale + bias);
         }
         swt[threadIdx.x] = w;
         __syncthreads();
@@ -421,7 +458,7 @@ __global__ void __launch_bounds__(128) k_sigattn_split(PassTables t, AttnBranch 
 template <typename OT>
 __global__ void k_sigattn_join(AttnBranch b, const float* __restrict__ part, int R, int splits, OT* __restrict__ out, int ld_out) {
     const int r = blockIdx.x, n = b.heads * b.vdim;
-    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
         float a = 0.0f;
         for (int k = 0; k < splits; k++) a += part[((size_t)k * R + r) * n + c];
         out[(size_t)r * ld_out + b.a_off + c] = cvt<OT>(a * b.out_scale);

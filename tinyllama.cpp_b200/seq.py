@@ -38,7 +38,7 @@ class ConfigC(C.Structure):
 
 SYMBOLS = ["gtb_seq_create", "gtb_seq_destroy", "gtb_seq_set_tensor", "gtb_seq_finalize", "gtb_seq_n_runs", "gtb_seq_slot_reset",
            "gtb_seq_slot_position", "gtb_seq_step", "gtb_seq_step_greedy", "gtb_seq_decode", "gtb_seq_topk", "gtb_seq_last_logits",
-           "gtb_seq_set_option", "gtb_seq_read_capture", "gtb_seq_weight_bytes", "gtb_seq_state_bytes_per_slot"]
+           "gtb_seq_set_option", "gtb_seq_read_capture", "gtb_seq_weight_bytes", "gtb_seq_state_bytes_per_slot", "gtb_seq_selftest_gemm"]
 
 _lib = None
 
@@ -61,6 +61,7 @@ def lib():
             "gtb_seq_step": [vp, i, vp, vp, vp, i, vp, vp], "gtb_seq_step_greedy": [vp, i, vp, vp, vp, vp],
             "gtb_seq_decode": [vp, i, vp, i, i, vp], "gtb_seq_topk": [vp, i, i, vp, vp], "gtb_seq_last_logits": [vp, i, vp],
             "gtb_seq_set_option": [vp, C.c_char_p, i], "gtb_seq_read_capture": [vp, i, i, vp],
+            "gtb_seq_selftest_gemm": [vp, vp, vp, i, i, i, i, i, i, C.POINTER(C.c_float)],
             "gtb_seq_weight_bytes": [vp, C.POINTER(sz)], "gtb_seq_state_bytes_per_slot": [vp, C.POINTER(sz)],
         }
         for name, args in sigs.items():
@@ -99,6 +100,16 @@ def _hp(a: np.ndarray):
 
 def _i32(a) -> np.ndarray:
     return np.ascontiguousarray(a, np.int32)
+
+
+def selftest_gemm(a_bits: np.ndarray, w_bits: np.ndarray, c0: np.ndarray | None = None, ld_extra: int = 0, iters: int = 1):
+    """The tcgen05 bf16 product on host operands (bfloat16 bit patterns): returns (A . W^T (+ c0), mean milliseconds of `iters` runs)."""
+    a, w = np.ascontiguousarray(a_bits, np.uint16), np.ascontiguousarray(w_bits, np.uint16)
+    (m, k), n = a.shape, w.shape[0]
+    c = np.zeros((m, n), np.float32) if c0 is None else np.ascontiguousarray(c0, np.float32).copy()
+    ms = C.c_float()
+    check(lib().gtb_seq_selftest_gemm(_hp(a), _hp(w), _hp(c), m, n, k, ld_extra, int(c0 is not None), iters, C.byref(ms)))
+    return c, ms.value
 
 
 class SeqModel:
