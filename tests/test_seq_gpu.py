@@ -252,6 +252,7 @@ def test_long_decoding(lib, mode):
     dict(vocab=33, width=40, ff=24, l_heads=1, l_kv=1, l_dim=40, l_vdim=8, r_heads=1, r_dim=4, r_vdim=40, rot_dims=2, taps=1),
     dict(vocab=130, width=136, ff=200, l_heads=8, l_kv=8, l_dim=8, l_vdim=24, r_heads=5, r_dim=32, r_vdim=8, rot_dims=32, taps=2, loop=(0, 1, 1)),
     dict(vocab=64, width=64, ff=64, l_heads=4, l_kv=1, l_dim=32, l_vdim=16, r_heads=2, r_dim=16, r_vdim=72, rot_dims=0, taps=7, n_layers=4, loop=(1, 4, 2), no_mlp=(2,)),
+    dict(vocab=64, width=64, ff=32, l_heads=2, l_kv=1, l_dim=136, l_vdim=200, r_heads=1, r_dim=520, r_vdim=72, rot_dims=40, n_layers=1),   # heads beyond the tiled kernels' sizes
 ])
 def test_other_sizes(lib, kw):
     cfg = small(**kw)

@@ -40,7 +40,7 @@ struct TensorDest {
 
 struct BranchW {
     gtb_seq_branch d{};
-    std::vector<float> decay;
+    std::vector<float> decay, inv_freq;
     int q_off = 0, k_off = 0, v_off = 0, g_off = 0, a_off = 0;
     int kq = 0, kk = 0, kv = 0;   // projection widths
     float* d_pb = nullptr;
@@ -203,13 +203,16 @@ int sigattn_mma(const PassTables& t, const AttnBranch& a, int S, int n_tiles, co
     return -1;
 }
 
-struct RetLaunch { dim3 block; size_t smem; };
+// row-by-row retention (decode rows, short portions): value channels per CTA, CTA shape, slices, shared memory
+struct RetLaunch { dim3 block; size_t smem; int vs, nvs; };
 RetLaunch ret_launch(const gtb_seq_branch& d) {
     RetLaunch r;
-    const int bx = (d.vdim + 31) / 32 * 32;
+    r.vs = std::min(d.vdim, d.dim > 512 ? 32 : 64);
+    r.nvs = (d.vdim + r.vs - 1) / r.vs;
+    const int bx = (r.vs + 31) / 32 * 32;
     int ny = std::max(1, std::min(std::min(512 / bx, d.dim), 16));
     r.block = dim3(bx, ny);
-    r.smem = ((size_t)d.dim * d.vdim + 4 * (size_t)d.dim + (size_t)ny * d.vdim) * sizeof(float);
+    r.smem = ((size_t)d.dim * r.vs + 4 * (size_t)d.dim + (size_t)ny * r.vs) * sizeof(float);
     return r;
 }
 
@@ -312,7 +315,7 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                 }
                 const RetLaunch rl = ret_launch(b.d);
                 if (rl.smem > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_retention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rl.smem));
-                k_retention<<<dim3(S, a.heads), rl.block, rl.smem, st>>>(t, a, m->P, l.n1, run.state[bi], m->O);
+                k_retention<<<dim3(S, a.heads, rl.nvs), rl.block, rl.smem, st>>>(t, a, m->P, l.n1, run.state[bi], m->O, rl.vs);
                 GTB_LAUNCHED();
                 k_ret_post<OT><<<dim3(R, (a.heads + 3) / 4), 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
                 GTB_LAUNCHED();
@@ -417,10 +420,11 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 TRY(dalloc_t(m, &b.d_decay, d.heads));
                 GTB_CUDA(cudaMemcpyAsync(b.d_decay, b.decay.data(), d.heads * sizeof(float), cudaMemcpyHostToDevice, ctx().stream));
                 if (d.rot_dims > 0) {
-                    std::vector<float> f(d.rot_dims / 2);
-                    for (int k = 0; k < d.rot_dims / 2; k++) f[k] = (float)pow((double)d.rot_base, -2.0 * k / d.rot_dims);
-                    TRY(dalloc_t(m, &b.d_inv_freq, f.size()));
-                    GTB_CUDA(cudaMemcpy(b.d_inv_freq, f.data(), f.size() * sizeof(float), cudaMemcpyHostToDevice));
+                    // (same stream as the allocation's zero fill: a copy on another stream could be overtaken by it)
+                    b.inv_freq.resize(d.rot_dims / 2);
+                    for (int k = 0; k < d.rot_dims / 2; k++) b.inv_freq[k] = (float)pow((double)d.rot_base, -2.0 * k / d.rot_dims);
+                    TRY(dalloc_t(m, &b.d_inv_freq, b.inv_freq.size()));
+                    GTB_CUDA(cudaMemcpyAsync(b.d_inv_freq, b.inv_freq.data(), b.inv_freq.size() * sizeof(float), cudaMemcpyHostToDevice, ctx().stream));
                 }
             }
         }
@@ -888,6 +892,7 @@ int gtb_seq_selftest_gemm(const void* h_A, const void* h_W, float* h_C, int M, i
     cudaMemcpy2D(dA, (size_t)ld * 2, h_A, (size_t)K * 2, (size_t)K * 2, M, cudaMemcpyHostToDevice);
     cudaMemcpy2D(dW, (size_t)ld * 2, h_W, (size_t)K * 2, (size_t)K * 2, N, cudaMemcpyHostToDevice);
     cudaMemcpy(dC, h_C, (size_t)M * N * 4, cudaMemcpyHostToDevice);
+    cudaDeviceSynchronize();          // the copies above ran on the default stream, the product runs on the library stream
     rc = seq_gemm_bf16(gp, dA, ld, dW, ld, dC, N, M, N, K, nullptr, accumulate);
     if (rc) return done(rc == -1 ? gtb::fail(GTB_ERR_ARG, "shape not supported by the tensor-core product") : rc);
     cudaMemcpyAsync(h_C, dC, (size_t)M * N * 4, cudaMemcpyDeviceToHost, st);

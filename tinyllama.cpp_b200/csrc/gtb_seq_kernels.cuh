@@ -476,23 +476,29 @@ struct RetBranch {
     int q_off, k_off, v_off, g_off;
     int a_off;
 };
-// One CTA per (segment, head) walks the segment's rows in order: S <- decay S + k v^T, o = S^T q.  The state [dim][vdim] sits in shared
-// memory for the walk (thread = value channel; row groups of the state are split over the y dimension of the CTA and summed through
-// shared memory), starts from and returns to the slot's state in HBM.  q and k are rotated (pairs i, i + rot_dims/2) and k scaled here.
+// One CTA per (segment, head, slice of value channels) walks the segment's rows in order: S <- decay S + k v^T, o = S^T q.  The columns of
+// the state are independent of each other, so a CTA keeps only its slice [dim][vs] in shared memory for the walk (thread x = value
+// channel; row groups of the state are split over the y dimension of the CTA and summed through shared memory); it starts from and
+// returns to the slot's state in HBM.  q and k are rotated (pairs i, i + rot_dims/2) and k scaled here.
 // raw o goes to O [R][heads * vdim] (fp32); normalisation and the gate follow in k_ret_post.
-__global__ void k_retention(PassTables t, RetBranch b, const float* __restrict__ P, int ldp, float* __restrict__ state, float* __restrict__ O) {
+__global__ void k_retention(PassTables t, RetBranch b, const float* __restrict__ P, int ldp, float* __restrict__ state, float* __restrict__ O, int vs) {
     extern __shared__ float sm[];
     const int s = blockIdx.x, h = blockIdx.y;
     const int slot = t.seg_slot[s], row0 = t.seg_row0[s], len = t.seg_len[s];
-    const int ny = blockDim.y, ty = threadIdx.y, j = threadIdx.x;       // blockDim.x >= vdim
-    const int tid = ty * blockDim.x + j, nt = blockDim.x * ny;
-    float* S = sm;                                   // [dim][vdim]
-    float* sq = S + (size_t)b.dim * b.vdim;          // [2][dim]
+    const int ny = blockDim.y, ty = threadIdx.y, jl = threadIdx.x;        // blockDim.x >= vs
+    const int j = blockIdx.z * vs + jl;                                   // value channel
+    const bool jok = jl < vs && j < b.vdim;
+    const int tid = ty * blockDim.x + jl, nt = blockDim.x * ny;
+    float* S = sm;                                   // [dim][vs]
+    float* sq = S + (size_t)b.dim * vs;              // [2][dim]
     float* sk = sq + 2 * b.dim;                      // [2][dim]
-    float* part = sk + 2 * b.dim;                    // [ny][vdim]
+    float* part = sk + 2 * b.dim;                    // [ny][vs]
     float* gs = state + ((size_t)slot * b.heads + h) * (size_t)b.dim * b.vdim;
     const bool live = !t.slots[slot].stopped;
-    for (int i = tid; i < b.dim * b.vdim; i += nt) S[i] = gs[i];
+    for (int e = tid; e < b.dim * vs; e += nt) {
+        const int i = e / vs, c = blockIdx.z * vs + e % vs;
+        S[e] = c < b.vdim ? gs[(size_t)i * b.vdim + c] : 0.0f;
+    }
     const float decay = b.decay[h];
     const int half = b.rot_dims / 2;
     const int i0 = (int)(((long long)b.dim * ty) / ny), i1 = (int)(((long long)b.dim * (ty + 1)) / ny);
@@ -516,26 +522,29 @@ __global__ void k_retention(PassTables t, RetBranch b, const float* __restrict__
             sk[buf * b.dim + i] = kv * b.scale;
         }
         __syncthreads();
-        if (j < b.vdim) {
+        if (jok) {
             const float v = p[b.v_off + h * b.vdim + j];
             float o = 0.0f;
             for (int i = i0; i < i1; i++) {
-                const float sv = fmaf(decay, S[(size_t)i * b.vdim + j], sk[buf * b.dim + i] * v);
-                S[(size_t)i * b.vdim + j] = sv;
+                const float sv = fmaf(decay, S[(size_t)i * vs + jl], sk[buf * b.dim + i] * v);
+                S[(size_t)i * vs + jl] = sv;
                 o = fmaf(sv, sq[buf * b.dim + i], o);
             }
-            part[ty * b.vdim + j] = o;
+            part[ty * vs + jl] = o;
         }
         __syncthreads();
-        if (ty == 0 && j < b.vdim) {
+        if (ty == 0 && jok) {
             float o = 0.0f;
-            for (int y = 0; y < ny; y++) o += part[y * b.vdim + j];
+            for (int y = 0; y < ny; y++) o += part[y * vs + jl];
             O[(size_t)r * (b.heads * b.vdim) + h * b.vdim + j] = o;
         }
     }
     __syncthreads();
     if (live)
-        for (int i = tid; i < b.dim * b.vdim; i += nt) gs[i] = S[i];
+        for (int e = tid; e < b.dim * vs; e += nt) {
+            const int i = e / vs, c = blockIdx.z * vs + e % vs;
+            if (c < b.vdim) gs[(size_t)i * b.vdim + c] = S[e];
+        }
 }
 // per (row, head): o / rms(o) (optional), * silu(gate) (optional), * out_scale -> operand of the out projection
 template <typename OT>

@@ -32,7 +32,7 @@ def describe(cfg: dict) -> dict:
     bg = (cfg.get("embedding") or {}).get("bigram")
     d["bigram"] = {k: int(bg[k]) for k in ("buckets", "mul_prev", "mul_cur")} if bg else None
     lp = cfg.get("loop")
-    d["loop"] = {k: int(lp[k]) for k in ("start", "stop", "times")} if lp and int(lp.get("times", 0)) > 0 else None
+    d["loop"] = {k: int(lp[k]) for k in ("start", "stop", "times")} if lp and int(lp.get("times", 0)) > 0 and int(lp["stop"]) > int(lp["start"]) else None
     for i, l in enumerate(cfg["layers"]):
         if l.get("type") != "parallel":
             raise ValueError(f"layer {i}: unknown type {l.get('type')!r}")
