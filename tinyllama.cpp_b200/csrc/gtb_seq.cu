@@ -82,6 +82,7 @@ struct gtb_seq_model {
     float *loop_step = nullptr, *final_gain = nullptr;
     // workspace of a pass
     int max_rows = 0, n1_max = 0, ff_max = 0, kout_p_max = 0, ro_max = 0;
+    float* Y = nullptr;                          // fresh output block of an accumulating tensor-core product [max_rows][width]
     float *x = nullptr, *x0 = nullptr, *h = nullptr, *P = nullptr, *G = nullptr, *O = nullptr, *logits = nullptr;
     void *opA = nullptr, *opB = nullptr, *opC = nullptr, *opL = nullptr, *opH = nullptr;
     float* attn_part = nullptr;                  // split decode attention: partial sums [splits][SPLIT_MAX_ROWS][heads * vdim]
@@ -142,7 +143,15 @@ int product(gtb_seq_model* m, const void* A, int lda, const bf16* W, int ldw, fl
     cudaStream_t st = ctx().stream;
     const OT* a = reinterpret_cast<const OT*>(A);
     if (sizeof(OT) == 2 && m->use_tensor && M >= m->tensor_min_rows && m->gp) {
-        int rc = seq_gemm_bf16(m->gp, A, lda, W, ldw, C, ldc, M, N, Kp, bias, acc);
+        // An accumulating epilogue reads C one row per thread (the TMEM lane layout): measured 4x the whole product's time.  So the
+        // tensor-core kernel always writes a fresh [M][N] block and a coalesced kernel adds it to the stream.
+        float* dst = (acc && N <= m->cfg.width) ? m->Y : C;
+        int rc = seq_gemm_bf16(m->gp, A, lda, W, ldw, dst, dst == C ? ldc : N, M, N, Kp, bias, dst == C ? acc : 0);
+        if (rc == 0 && dst != C) {
+            const size_t n4 = (size_t)M * N;
+            k_add_block<<<(unsigned)((n4 + 255) / 256), 256, 0, st>>>(C, ldc, m->Y, N, M);
+            GTB_LAUNCHED();
+        }
         if (rc != -1) return rc;                 // -1: shape not supported by that kernel
     }
     if (M <= 8) {
@@ -178,10 +187,10 @@ struct RetChunk { int C, vs; size_t smem_kv, smem_out; bool ok; };
 RetChunk ret_chunk(const gtb_seq_branch& d) {
     RetChunk r;
     r.C = d.dim <= 128 ? 64 : 32;
-    r.vs = std::min(d.vdim, 64);
+    r.vs = std::min(d.vdim, r.C);         // a state slice [dim][vs] must fit where the keys [dim][C] were
     const size_t dp = (d.dim + 3) & ~3, vsp = (r.vs + 3) & ~3;
     r.smem_kv = ((size_t)r.C * dp + (size_t)r.C * vsp) * sizeof(float);
-    r.smem_out = (2 * (size_t)r.C * d.dim + (size_t)r.C * vsp + (size_t)r.C * r.C + (size_t)d.dim * vsp) * sizeof(float);
+    r.smem_out = (2 * (size_t)r.C * d.dim + (size_t)r.C * vsp + (size_t)r.C * r.C) * sizeof(float);     // the incoming state reuses the keys' space
     r.ok = r.smem_out <= 200 * 1024;
     return r;
 }
@@ -511,6 +520,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     TRY(dalloc_t(m, &m->x, R * W));
     TRY(dalloc_t(m, &m->x0, R * W));
     TRY(dalloc_t(m, &m->h, R * W));
+    TRY(dalloc_t(m, &m->Y, R * W));
     TRY(dalloc_t(m, &m->P, R * m->n1_max));
     TRY(dalloc_t(m, &m->G, R * 2 * std::max(m->ff_max, 1)));
     TRY(dalloc_t(m, &m->O, R * std::max(m->ro_max, 1)));
@@ -898,10 +908,29 @@ int gtb_seq_selftest_gemm(const void* h_A, const void* h_W, float* h_C, int M, i
     cudaMemcpyAsync(h_C, dC, (size_t)M * N * 4, cudaMemcpyDeviceToHost, st);
     cudaEventCreate(&e0); cudaEventCreate(&e1);
     cudaEventRecord(e0, st);
-    for (int i = 0; i < iters; i++) seq_gemm_bf16(gp, dA, ld, dW, ld, dC, N, M, N, K, nullptr, 0);
+    // accumulate >= 2: timing runs accumulate too and a 256 MB buffer is rewritten before each (operands come from HBM, not L2)
+    void* flush = nullptr;
+    float total = 0.0f;
+    if (accumulate >= 2 && cudaMalloc(&flush, (size_t)256 << 20) != cudaSuccess) flush = nullptr;
+    if (flush) {
+        for (int i = 0; i < iters; i++) {
+            cudaMemsetAsync(flush, i, (size_t)256 << 20, st);
+            cudaEventRecord(e0, st);
+            seq_gemm_bf16(gp, dA, ld, dW, ld, dC, N, M, N, K, nullptr, 1);
+            cudaEventRecord(e1, st);
+            cudaStreamSynchronize(st);
+            float t = 0.0f;
+            cudaEventElapsedTime(&t, e0, e1);
+            total += t;
+        }
+        cudaFree(flush);
+        cudaEventRecord(e0, st);
+    } else {
+        for (int i = 0; i < iters; i++) seq_gemm_bf16(gp, dA, ld, dW, ld, dC, N, M, N, K, nullptr, 0);
+    }
     cudaEventRecord(e1, st);
     if (cudaStreamSynchronize(st) != cudaSuccess) return done(gtb::fail(GTB_ERR_CUDA, "the product failed: %s", cudaGetErrorString(cudaGetLastError())));
-    if (ms) { cudaEventElapsedTime(ms, e0, e1); *ms /= iters; }
+    if (ms) { cudaEventElapsedTime(ms, e0, e1); *ms = (flush ? total : *ms) / iters; }
     int bad = 0;
     seq_gemm_status(gp, &bad);
     return done(bad ? gtb::fail(GTB_ERR_STATE, "the product gave up on a pipeline wait") : GTB_OK);

@@ -578,6 +578,13 @@ __global__ void k_geglu(const float* __restrict__ G, int ff, OT* __restrict__ ou
     const int gc = interleaved ? (c >> 5) * 64 + (c & 31) : c, uc = interleaved ? gc + 32 : ff + c;
     out[(size_t)r * ld_out + a_off + c] = cvt<OT>(gelu_tanh(G[(size_t)r * 2 * ff + gc]) * G[(size_t)r * 2 * ff + uc]);
 }
+// C[r][c] += Y[r][c] for an [M][N] block (N contiguous in Y)
+__global__ void k_add_block(float* __restrict__ C, int ldc, const float* __restrict__ Y, int N, int M) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (size_t)M * N) return;
+    const size_t r = i / N, c = i % N;
+    C[r * ldc + c] += Y[i];
+}
 // operand [x | x0] of the loop's entry projection
 template <typename OT>
 __global__ void k_concat2(const float* __restrict__ x, const float* __restrict__ x0, int width, OT* __restrict__ out, int ld_out) {
@@ -747,10 +754,10 @@ __global__ void __launch_bounds__(256) k_ret_chunk_out(PassTables t, RetBranch b
     const int row0 = t.seg_row0[seg] + c * C, L = min(C, t.seg_len[seg] - c * C);
     const int vsp = (vs + 3) & ~3;
     float* sq = sm;                       // [dim][C]
-    float* sk = sq + b.dim * C;           // [dim][C]
+    float* sk = sq + b.dim * C;           // [dim][C]; the same space holds s0 [dim][vsp] once the key products are done (vsp <= C)
     float* sv = sk + b.dim * C;           // [C][vsp]
     float* sa = sv + C * vsp;             // [C][C]
-    float* s0 = sa + C * C;               // [dim][vsp]
+    float* s0 = sk;
     const float lg = logf(b.decay[h]);
     for (int e = threadIdx.x; e < C * b.dim; e += blockDim.x) {
         const int bb = e % C, i = e / C;
@@ -766,11 +773,6 @@ __global__ void __launch_bounds__(256) k_ret_chunk_out(PassTables t, RetBranch b
     for (int e = threadIdx.x; e < C * vsp; e += blockDim.x) {
         const int bb = e / vsp, j = e % vsp;
         sv[e] = (bb < L && j < nv) ? P[(size_t)(row0 + bb) * ldp + b.v_off + h * b.vdim + j0 + j] : 0.0f;
-    }
-    const float* sb = Sb + (((size_t)blockIdx.x * b.heads + h) * b.dim) * b.vdim;
-    for (int e = threadIdx.x; e < b.dim * vsp; e += blockDim.x) {
-        const int i = e / vsp, j = e % vsp;
-        s0[e] = j < nv ? sb[(size_t)i * b.vdim + j0 + j] : 0.0f;
     }
     __syncthreads();
     const int tc = C / 4;
@@ -795,6 +797,12 @@ __global__ void __launch_bounds__(256) k_ret_chunk_out(PassTables t, RetBranch b
                 const int a = a4 + x, bb = b4 + y;
                 sa[bb * C + a] = (bb <= a) ? acc[y][x] * expf(lg * (float)(a - bb)) : 0.0f;
             }
+    }
+    __syncthreads();
+    const float* sb = Sb + (((size_t)blockIdx.x * b.heads + h) * b.dim) * b.vdim;
+    for (int e = threadIdx.x; e < b.dim * vsp; e += blockDim.x) {
+        const int i = e / vsp, j = e % vsp;
+        s0[e] = j < nv ? sb[(size_t)i * b.vdim + j0 + j] : 0.0f;
     }
     __syncthreads();
     const int tj = vsp / 4;
@@ -852,6 +860,9 @@ __device__ __forceinline__ uint32_t sa_pack(float lo, float hi) {
     const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<const uint32_t*>(&v);
 }
+// sigmoid from the special-function unit's exp2 and reciprocal: relative error of a few ulp also for tiny weights (the weights are
+// rounded to bf16 right after)
+__device__ __forceinline__ float sa_sigmoid(float z) { return __fdividef(1.0f, 1.0f + __expf(-z)); }
 __device__ __forceinline__ bool sa_find_tile(const PassTables& t, int S, int idx, int& seg, int& q0) {
     for (int s = 0; s < S; s++) {
         const int n = (t.seg_len[s] + 63) / 64;
@@ -938,10 +949,10 @@ __global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b,
 #pragma unroll
         for (int n = 0; n < 8; n++) {
             const int key = j0 + n * 8 + tq * 2;
-            const float w0 = key <= p_lo ? sigmoidf_(sc[n][0] * b.scale + bias) : 0.0f;
-            const float w1 = key + 1 <= p_lo ? sigmoidf_(sc[n][1] * b.scale + bias) : 0.0f;
-            const float w2 = key <= p_hi ? sigmoidf_(sc[n][2] * b.scale + bias) : 0.0f;
-            const float w3 = key + 1 <= p_hi ? sigmoidf_(sc[n][3] * b.scale + bias) : 0.0f;
+            const float w0 = key <= p_lo ? sa_sigmoid(sc[n][0] * b.scale + bias) : 0.0f;
+            const float w1 = key + 1 <= p_lo ? sa_sigmoid(sc[n][1] * b.scale + bias) : 0.0f;
+            const float w2 = key <= p_hi ? sa_sigmoid(sc[n][2] * b.scale + bias) : 0.0f;
+            const float w3 = key + 1 <= p_hi ? sa_sigmoid(sc[n][3] * b.scale + bias) : 0.0f;
             w[n][0] = sa_pack(w0, w1);
             w[n][1] = sa_pack(w2, w3);
         }
