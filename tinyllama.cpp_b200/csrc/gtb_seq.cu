@@ -105,6 +105,7 @@ struct gtb_seq_model {
     int tensor_min_rows = 64;
     bool use_graph = true;
     bool fused_attn = true;
+    bool fused_norm = true;
     SeqGemmPlan* gp = nullptr;
     // decode graph
     cudaGraphExec_t graph = nullptr;
@@ -197,7 +198,7 @@ RetChunk ret_chunk(const gtb_seq_branch& d) {
 
 template <int DP, int VP>
 int launch_sigattn_mma(const PassTables& t, const AttnBranch& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, bf16* out, int ld_out) {
-    const size_t smem = (2 * 64 * (size_t)(DP + 8) + 64 * (size_t)(VP + 8)) * 2;
+    const size_t smem = (3 * 64 * (size_t)(DP + 8) + 2 * 64 * (size_t)(VP + 8)) * 2;      // queries + two stages of keys and values
     static bool attr = false;
     if (!attr) { GTB_CUDA(cudaFuncSetAttribute(k_sigattn_mma<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
     k_sigattn_mma<DP, VP><<<dim3(n_tiles, a.heads), 128, smem, ctx().stream>>>(t, a, S, P, ldp, kc, vc, out, ld_out);
@@ -249,12 +250,19 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
             int rc = product<OT>(m, opL, pad64(2 * W), m->loop_in, pad64(2 * W), m->x, W, R, W, pad64(2 * W), m->loop_step + (size_t)run.pass * W, 0);
             if (rc) return rc;
         }
-        k_rmsnorm_scalar<float><<<R, 256, 0, st>>>(m->x, W, c.eps, l.d_gain, nullptr, m->h, W);
-        GTB_LAUNCHED();
         OT* ob = l.ff > 0 ? opB : nullptr;
-        if (c.taps > 0) {
-            k_canon<OT><<<dim3(R, (W + 255) / 256), 256, 0, st>>>(t, m->h, W, c.taps, l.canon_a, l.ff > 0 ? l.canon_b : nullptr, run.tail, opA, ob, wp);
+        if (c.taps > 0 && c.taps <= 32 && m->fused_norm) {
+            k_norm_canon<OT><<<R, 256, 0, st>>>(t, m->x, W, c.eps, l.d_gain, c.taps, l.canon_a, l.ff > 0 ? l.canon_b : nullptr, run.tail, m->h, opA, ob, wp);
             GTB_LAUNCHED();
+        } else {
+            k_rmsnorm_scalar<float><<<R, 256, 0, st>>>(m->x, W, c.eps, l.d_gain, nullptr, m->h, W);
+            GTB_LAUNCHED();
+        }
+        if (c.taps > 0) {
+            if (!(c.taps <= 32 && m->fused_norm)) {
+                k_canon<OT><<<dim3(R, (W + 255) / 256), 256, 0, st>>>(t, m->h, W, c.taps, l.canon_a, l.ff > 0 ? l.canon_b : nullptr, run.tail, opA, ob, wp);
+                GTB_LAUNCHED();
+            }
             if (c.taps > 1) {
                 k_canon_tail<<<dim3(S, (W + 255) / 256), 256, 0, st>>>(t, m->h, W, c.taps, run.tail);
                 GTB_LAUNCHED();
@@ -869,6 +877,7 @@ int gtb_seq_set_option(gtb_seq_t m, const char* name, int value) {
     else if (n == "tensor_min_rows") m->tensor_min_rows = std::max(1, value);
     else if (n == "graph") m->use_graph = value != 0;
     else if (n == "fused_attn") m->fused_attn = value != 0;
+    else if (n == "fused_norm") m->fused_norm = value != 0;
     else return gtb::fail(GTB_ERR_ARG, "unknown option '%s'", name);
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return GTB_OK;

@@ -194,9 +194,22 @@ k_seq_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                         const int c0 = col >> 1;                   // first of the 32 activation channels
                         __nv_bfloat16* dst = ep.act + (size_t)row * ep.ld_act + ep.act_off + c0;
                         const int nc = min(32, (N >> 1) - c0);
+                        if (nc == 32 && ((((uintptr_t)dst) & 15) == 0)) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (j < nc) dst[j] = __float2bfloat16_rn(sq_gelu(g[j]) * u[j]);
+                            for (int j = 0; j < 32; j += 8) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    const __nv_bfloat162 v = __floats2bfloat162_rn(sq_gelu(g[j + 2 * q]) * u[j + 2 * q], sq_gelu(g[j + 2 * q + 1]) * u[j + 2 * q + 1]);
+                                    w[q] = *reinterpret_cast<const uint32_t*>(&v);
+                                }
+                                *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (j < nc) dst[j] = __float2bfloat16_rn(sq_gelu(g[j]) * u[j]);
+                        }
                     }
                 }
             }

@@ -176,6 +176,42 @@ __global__ void k_canon(PassTables t, const float* __restrict__ h, int width, in
         if (out_b) out_b[(size_t)r * ld_out + c] = cvt<OT>(hc + b);
     }
 }
+// Norm and convolution in one kernel: a CTA owns row r; its warps first compute 1 / rms of the `taps` rows the convolution reaches
+// back to (those inside the segment), then every thread forms h of its channels for those rows on the fly.  h of the row itself
+// is also written out (the history update and the capture read it).  taps <= 32.
+template <typename OT>
+__global__ void __launch_bounds__(256) k_norm_canon(PassTables t, const float* __restrict__ x, int width, float eps, const float* __restrict__ g, int taps,
+                                                    const bf16* __restrict__ wa, const bf16* __restrict__ wb, const float* __restrict__ tail,
+                                                    float* __restrict__ h, OT* __restrict__ out_a, OT* __restrict__ out_b, int ld_out) {
+    __shared__ float inv[32];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    const int s = t.row_seg[r], row0 = t.seg_row0[s], slot = t.seg_slot[s];
+    const float gain = g[0];
+    for (int j = wid; j < taps; j += nw) {
+        const int src = r - (taps - 1) + j;
+        if (src < row0) continue;                          // warp-uniform
+        const float* xr = x + (size_t)src * width;
+        float ss = 0.0f;
+        for (int c = lane; c < width; c += 32) { const float v = xr[c]; ss += v * v; }
+        ss = warp_sum(ss);
+        if (lane == 0) inv[j] = (1.0f / sqrtf(ss / (float)width + eps)) * gain;
+    }
+    __syncthreads();
+    const float* tl = tail + (size_t)slot * (taps - 1) * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float a = 0.0f, b = 0.0f, hc = 0.0f;
+        for (int j = 0; j < taps; j++) {
+            const int src = r - (taps - 1) + j;
+            const float v = (src >= row0) ? x[(size_t)src * width + c] * inv[j] : tl[(size_t)(src - row0 + taps - 1) * width + c];
+            a += __bfloat162float(wa[(size_t)c * taps + j]) * v;
+            if (wb) b += __bfloat162float(wb[(size_t)c * taps + j]) * v;
+            hc = v;
+        }
+        h[(size_t)r * width + c] = hc;
+        out_a[(size_t)r * ld_out + c] = cvt<OT>(hc + a);
+        if (out_b) out_b[(size_t)r * ld_out + c] = cvt<OT>(hc + b);
+    }
+}
 // no convolution configured: the operand is h itself
 template <typename OT>
 __global__ void k_copy_operand(const float* __restrict__ h, int width, OT* __restrict__ out_a, OT* __restrict__ out_b, int ld_out) {
@@ -872,14 +908,20 @@ __device__ __forceinline__ bool sa_find_tile(const PassTables& t, int S, int idx
     return false;
 }
 
+// 16-byte asynchronous copy global -> shared; !valid: the destination is filled with zeros
+__device__ __forceinline__ void sa_cp16(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
+
 template <int DP, int VP>
 __global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b, int S, const float* __restrict__ P, int ldp, const bf16* __restrict__ kc,
                                                      const bf16* __restrict__ vc, bf16* __restrict__ out, int ld_out) {
     constexpr int LQ = DP + 8, LV = VP + 8;
     extern __shared__ __align__(16) unsigned char sa_raw[];
     bf16* sq = reinterpret_cast<bf16*>(sa_raw);          // [64][LQ]
-    bf16* sk = sq + 64 * LQ;                            // [64][LQ]
-    bf16* sv = sk + 64 * LQ;                            // [64][LV]
+    bf16* sk0 = sq + 64 * LQ;                           // [2][64][LQ]: key tiles, double-buffered
+    bf16* sv0 = sk0 + 2 * 64 * LQ;                      // [2][64][LV]
     int seg, q0;
     if (!sa_find_tile(t, S, blockIdx.x, seg, q0)) return;
     const int h = blockIdx.y, g = h / (b.heads / b.kv_heads);
@@ -899,22 +941,23 @@ __global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b,
 #pragma unroll
     for (int n = 0; n < VP / 8; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
     const int last = pos0 + nq - 1;                      // last key any row of the tile sees
-    const uint32_t sq_a = (uint32_t)__cvta_generic_to_shared(sq), sk_a = (uint32_t)__cvta_generic_to_shared(sk), sv_a = (uint32_t)__cvta_generic_to_shared(sv);
-    for (int j0 = 0; j0 <= last; j0 += 64) {
-        __syncthreads();                                 // the previous tile's fragments have been read
+    const uint32_t sq_a = (uint32_t)__cvta_generic_to_shared(sq);
+    // tile j0 -> stage st: asynchronous 16-byte copies when the cache rows are 16-byte aligned, plain loads otherwise
+    auto load_tile = [&](int st, int j0) {
+        bf16* sk = sk0 + st * 64 * LQ;
+        bf16* sv = sv0 + st * 64 * LV;
         const int nk = min(64, last + 1 - j0);
         if (vec) {
+            const uint32_t ka = (uint32_t)__cvta_generic_to_shared(sk), va = (uint32_t)__cvta_generic_to_shared(sv);
             for (int e = threadIdx.x; e < 64 * (DP / 8); e += 128) {
                 const int r = e / (DP / 8), c8 = (e % (DP / 8)) * 8;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (r < nk && c8 < b.dim) v = *reinterpret_cast<const uint4*>(kbase + (size_t)(j0 + r) * kld + c8);
-                *reinterpret_cast<uint4*>(sk + r * LQ + c8) = v;
+                const bool ok = r < nk && c8 < b.dim;
+                sa_cp16(ka + (uint32_t)((r * LQ + c8) * 2), ok ? (const void*)(kbase + (size_t)(j0 + r) * kld + c8) : (const void*)kbase, ok);
             }
             for (int e = threadIdx.x; e < 64 * (VP / 8); e += 128) {
                 const int r = e / (VP / 8), c8 = (e % (VP / 8)) * 8;
-                uint4 v = make_uint4(0, 0, 0, 0);
-                if (r < nk && c8 < b.vdim) v = *reinterpret_cast<const uint4*>(vbase + (size_t)(j0 + r) * vld + c8);
-                *reinterpret_cast<uint4*>(sv + r * LV + c8) = v;
+                const bool ok = r < nk && c8 < b.vdim;
+                sa_cp16(va + (uint32_t)((r * LV + c8) * 2), ok ? (const void*)(vbase + (size_t)(j0 + r) * vld + c8) : (const void*)vbase, ok);
             }
         } else {
             for (int e = threadIdx.x; e < 64 * DP; e += 128) {
@@ -926,8 +969,19 @@ __global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b,
                 sv[r * LV + i] = (r < nk && i < b.vdim) ? vbase[(size_t)(j0 + r) * vld + i] : __float2bfloat16_rn(0.0f);
             }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile(0, 0);
+    int it = 0;
+    for (int j0 = 0; j0 <= last; j0 += 64, it++) {
+        const int st = it & 1;
+        const bool more = j0 + 64 <= last;
+        if (more) load_tile(st ^ 1, j0 + 64);            // its previous reader passed the barrier at the end of the last iteration
+        if (more) asm volatile("cp.async.wait_group 1;" ::: "memory");
+        else asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
-        if (j0 > pos0 + warp * 16 + 15) continue;        // every key of the tile lies after this warp's rows
+        const uint32_t sk_a = (uint32_t)__cvta_generic_to_shared(sk0 + st * 64 * LQ), sv_a = (uint32_t)__cvta_generic_to_shared(sv0 + st * 64 * LV);
+        if (j0 > pos0 + warp * 16 + 15) { __syncthreads(); continue; }        // every key of the tile lies after this warp's rows
         float sc[8][4];
 #pragma unroll
         for (int n = 0; n < 8; n++) { sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f; }
@@ -967,6 +1021,7 @@ __global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b,
                 sa_mma(o[2 * n2 + 1], a, b2, b3);
             }
         }
+        __syncthreads();                                 // this stage may be refilled from the next iteration on
     }
     const int r_lo = warp * 16 + gq, r_hi = r_lo + 8;
 #pragma unroll
