@@ -106,6 +106,7 @@ struct gtb_seq_model {
     bool use_graph = true;
     bool fused_attn = true;
     bool fused_norm = true;
+    bool group_decode = true;
     SeqGemmPlan* gp = nullptr;
     // decode graph
     cudaGraphExec_t graph = nullptr;
@@ -196,18 +197,21 @@ RetChunk ret_chunk(const gtb_seq_branch& d) {
     return r;
 }
 
-template <int DP, int VP>
+template <int DP, int VP, int HPC>
 int launch_sigattn_mma(const PassTables& t, const AttnBranch& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, bf16* out, int ld_out) {
-    const size_t smem = (3 * 64 * (size_t)(DP + 8) + 2 * 64 * (size_t)(VP + 8)) * 2;      // queries + two stages of keys and values
+    const size_t smem = ((HPC + 2) * 64 * (size_t)(DP + 8) + 2 * 64 * (size_t)(VP + 8)) * 2;      // queries + two stages of keys and values
     static bool attr = false;
-    if (!attr) { GTB_CUDA(cudaFuncSetAttribute(k_sigattn_mma<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
-    k_sigattn_mma<DP, VP><<<dim3(n_tiles, a.heads), 128, smem, ctx().stream>>>(t, a, S, P, ldp, kc, vc, out, ld_out);
+    if (!attr) { GTB_CUDA(cudaFuncSetAttribute(k_sigattn_mma<DP, VP, HPC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
+    k_sigattn_mma<DP, VP, HPC><<<dim3(n_tiles, a.heads / HPC), 128 * HPC, smem, ctx().stream>>>(t, a, S, P, ldp, kc, vc, out, ld_out);
     GTB_LAUNCHED();
     return GTB_OK;
 }
 int sigattn_mma(const PassTables& t, const AttnBranch& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, bf16* out, int ld_out) {
     const int dp = a.dim <= 32 ? 32 : a.dim <= 64 ? 64 : 128, vp = a.vdim <= 32 ? 32 : a.vdim <= 64 ? 64 : 128;
-#define SA_CASE(D, V) if (dp == D && vp == V) return launch_sigattn_mma<D, V>(t, a, S, n_tiles, P, ldp, kc, vc, out, ld_out)
+    // two query heads of a group can share a CTA's K/V tiles (HPC = 2): measured equal to one head per CTA at 32 heads x 2048 rows, so off
+    const bool pair = false && (a.heads / a.kv_heads) % 2 == 0 && dp <= 64 && vp <= 64;
+#define SA_CASE(D, V) if (dp == D && vp == V) return pair ? launch_sigattn_mma<D, V, 2>(t, a, S, n_tiles, P, ldp, kc, vc, out, ld_out) \
+                                                              : launch_sigattn_mma<D, V, 1>(t, a, S, n_tiles, P, ldp, kc, vc, out, ld_out)
     SA_CASE(32, 32); SA_CASE(32, 64); SA_CASE(32, 128); SA_CASE(64, 32); SA_CASE(64, 64); SA_CASE(64, 128); SA_CASE(128, 32); SA_CASE(128, 64); SA_CASE(128, 128);
 #undef SA_CASE
     return -1;
@@ -251,7 +255,8 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
             if (rc) return rc;
         }
         OT* ob = l.ff > 0 ? opB : nullptr;
-        if (c.taps > 0 && c.taps <= 32 && m->fused_norm) {
+        const bool nc_fused = c.taps > 0 && c.taps <= 8 && m->fused_norm && R >= 32;     // few rows: two kernels with channel-wide grids are quicker
+        if (nc_fused) {
             k_norm_canon<OT><<<R, 256, 0, st>>>(t, m->x, W, c.eps, l.d_gain, c.taps, l.canon_a, l.ff > 0 ? l.canon_b : nullptr, run.tail, m->h, opA, ob, wp);
             GTB_LAUNCHED();
         } else {
@@ -259,7 +264,7 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
             GTB_LAUNCHED();
         }
         if (c.taps > 0) {
-            if (!(c.taps <= 32 && m->fused_norm)) {
+            if (!nc_fused) {
                 k_canon<OT><<<dim3(R, (W + 255) / 256), 256, 0, st>>>(t, m->h, W, c.taps, l.canon_a, l.ff > 0 ? l.canon_b : nullptr, run.tail, opA, ob, wp);
                 GTB_LAUNCHED();
             }
@@ -297,7 +302,15 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                     done = sigattn_mma(t, a, S, n_qtiles, m->P, l.n1, (const bf16*)run.kc[bi], (const bf16*)run.vc[bi], (bf16*)opC, l.kout_p);
                 if (done > 0) return done;
                 if (done < 0 && !portions && m->attn_splits > 1 && R <= SPLIT_MAX_ROWS) {
-                    k_sigattn_split<OT><<<dim3(R, a.heads, m->attn_splits), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], m->attn_part, R);
+                    const int hg = a.heads / a.kv_heads;
+                    const int hc = std::max(1, std::min(std::min(hg, 8), 1024 / a.vdim));     // query heads per CTA: at most 8 outputs per thread
+                    if (hg > 1 && hc > 1 && m->group_decode) {
+                        const int chunks = (hg + hc - 1) / hc;
+                        k_sigattn_split_group<OT><<<dim3(R, a.kv_heads * chunks, m->attn_splits), 128, (size_t)hc * (a.dim + 128) * sizeof(float), st>>>(
+                            t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], m->attn_part, R, hc);
+                    } else {
+                        k_sigattn_split<OT><<<dim3(R, a.heads, m->attn_splits), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], m->attn_part, R);
+                    }
                     GTB_LAUNCHED();
                     k_sigattn_join<OT><<<dim3(R, (a.heads * a.vdim + 255) / 256), 256, 0, st>>>(a, m->attn_part, R, m->attn_splits, opC, l.kout_p);
                     GTB_LAUNCHED();
@@ -878,6 +891,7 @@ int gtb_seq_set_option(gtb_seq_t m, const char* name, int value) {
     else if (n == "graph") m->use_graph = value != 0;
     else if (n == "fused_attn") m->fused_attn = value != 0;
     else if (n == "fused_norm") m->fused_norm = value != 0;
+    else if (n == "group_decode") m->group_decode = value != 0;
     else return gtb::fail(GTB_ERR_ARG, "unknown option '%s'", name);
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return GTB_OK;

@@ -178,23 +178,34 @@ __global__ void k_canon(PassTables t, const float* __restrict__ h, int width, in
 }
 // Norm and convolution in one kernel: a CTA owns row r; its warps first compute 1 / rms of the `taps` rows the convolution reaches
 // back to (those inside the segment), then every thread forms h of its channels for those rows on the fly.  h of the row itself
-// is also written out (the history update and the capture read it).  taps <= 32.
+// is also written out (the history update reads it).
 template <typename OT>
 __global__ void __launch_bounds__(256) k_norm_canon(PassTables t, const float* __restrict__ x, int width, float eps, const float* __restrict__ g, int taps,
                                                     const bf16* __restrict__ wa, const bf16* __restrict__ wb, const float* __restrict__ tail,
                                                     float* __restrict__ h, OT* __restrict__ out_a, OT* __restrict__ out_b, int ld_out) {
-    __shared__ float inv[32];
-    const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    constexpr int MT = 8;                                   // taps <= MT (the host picks the two-kernel path otherwise)
+    __shared__ float red[8][MT];
+    __shared__ float inv[MT];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int s = t.row_seg[r], row0 = t.seg_row0[s], slot = t.seg_slot[s];
-    const float gain = g[0];
-    for (int j = wid; j < taps; j += nw) {
-        const int src = r - (taps - 1) + j;
-        if (src < row0) continue;                          // warp-uniform
-        const float* xr = x + (size_t)src * width;
-        float ss = 0.0f;
-        for (int c = lane; c < width; c += 32) { const float v = xr[c]; ss += v * v; }
-        ss = warp_sum(ss);
-        if (lane == 0) inv[j] = (1.0f / sqrtf(ss / (float)width + eps)) * gain;
+    const int first = max(0, row0 - (r - (taps - 1)));      // taps [first, taps) lie inside the segment
+    float ss[MT];
+#pragma unroll
+    for (int j = 0; j < MT; j++) ss[j] = 0.0f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+#pragma unroll
+        for (int j = 0; j < MT; j++)
+            if (j >= first && j < taps) { const float v = x[(size_t)(r - (taps - 1) + j) * width + c]; ss[j] = fmaf(v, v, ss[j]); }
+#pragma unroll
+    for (int j = 0; j < MT; j++) {
+        const float v = warp_sum(ss[j]);
+        if (lane == 0) red[wid][j] = v;
+    }
+    __syncthreads();
+    if (threadIdx.x < taps) {
+        float v = 0.0f;
+        for (int w = 0; w < 8; w++) v += red[w][threadIdx.x];
+        inv[threadIdx.x] = (1.0f / sqrtf(v / (float)width + eps)) * g[0];
     }
     __syncthreads();
     const float* tl = tail + (size_t)slot * (taps - 1) * width;
@@ -489,6 +500,83 @@ __global__ void __launch_bounds__(128) k_sigattn_split(PassTables t, AttnBranch 
     for (int cc = 0; cc < 4; cc++) {
         const int c = threadIdx.x + cc * blockDim.x;
         if (c < b.vdim) part[((size_t)blockIdx.z * R + r) * (b.heads * b.vdim) + h * b.vdim + c] = acc[cc];
+    }
+}
+// The same split, group-major: a CTA takes a key range for up to 8 query heads that share one K/V head.  A thread reads its key's row
+// once and scores it against all of the group's queries; in the value phase a thread owns (4 heads x 1 channel)-like slices of the
+// group's outputs, so each cached value is read once per 4 heads instead of once per head.
+constexpr int SG_MAXH = 8;          // query heads per CTA
+template <typename OT>
+__global__ void __launch_bounds__(128) k_sigattn_split_group(PassTables t, AttnBranch b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc,
+                                                             const OT* __restrict__ vc, float* __restrict__ part, int R, int hc) {
+    extern __shared__ float sm[];
+    const int hg = b.heads / b.kv_heads;                 // query heads per K/V head
+    const int chunks = (hg + hc - 1) / hc;               // CTAs per group along y (hc heads each)
+    const int r = blockIdx.x, g = blockIdx.y / chunks, h0 = g * hg + (blockIdx.y % chunks) * hc, nh = min(hc, g * hg + hg - h0);
+    float* sq = sm;                                      // [hc][dim]
+    float* swt = sm + hc * b.dim;                        // [hc][128]
+    const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
+    const int per = ((pos + 1 + (int)gridDim.z - 1) / (int)gridDim.z + 127) / 128 * 128;
+    const int lo = blockIdx.z * per, hi = min(pos + 1, lo + per);
+    for (int e = threadIdx.x; e < nh * b.dim; e += 128) sq[e] = P[(size_t)r * ldp + b.q_off + (size_t)h0 * b.dim + e];
+    const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
+    const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
+    const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
+    const int nout = nh * b.vdim;                        // outputs of this CTA: (head, channel), at most 8 per thread
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) acc[i] = 0.0f;
+    __syncthreads();
+    for (int j0 = lo; j0 < hi; j0 += 128) {
+        const int j = j0 + threadIdx.x;
+        float sc[SG_MAXH];
+#pragma unroll
+        for (int hh = 0; hh < SG_MAXH; hh++) sc[hh] = 0.0f;
+        if (j < hi) {
+            const OT* kr = kbase + (size_t)j * kld;
+            if (b.dim % 8 == 0) {                        // rows of the cache start on 16-byte boundaries then
+                for (int i = 0; i < b.dim; i += 8) {
+                    float kv[8];
+                    load8<OT>(kr + i, kv);
+#pragma unroll
+                    for (int hh = 0; hh < SG_MAXH; hh++)
+                        if (hh < nh) {
+#pragma unroll
+                            for (int q = 0; q < 8; q++) sc[hh] = fmaf(sq[hh * b.dim + i + q], kv[q], sc[hh]);
+                        }
+                }
+            } else {
+                for (int i = 0; i < b.dim; i++) {
+                    const float kv = ldf<OT>(kr + i);
+#pragma unroll
+                    for (int hh = 0; hh < SG_MAXH; hh++)
+                        if (hh < nh) sc[hh] = fmaf(sq[hh * b.dim + i], kv, sc[hh]);
+                }
+            }
+        }
+#pragma unroll
+        for (int hh = 0; hh < SG_MAXH; hh++)
+            if (hh < nh) swt[hh * 128 + threadIdx.x] = (j < hi) ? sigmoidf_(sc[hh] * b.scale + (b.pb ? b.pb[h0 + hh] : 0.0f)) : 0.0f;
+        __syncthreads();
+        const int nj = min(128, hi - j0);
+#pragma unroll
+        for (int oo = 0; oo < 8; oo++) {
+            const int o = threadIdx.x + oo * 128;
+            if (o < nout) {
+                const int hh = o / b.vdim, c = o % b.vdim;
+                float a = acc[oo];
+                const OT* vr = vbase + (size_t)j0 * vld + c;
+                const float* w = swt + hh * 128;
+                for (int jj = 0; jj < nj; jj++) a = fmaf(w[jj], ldf<OT>(vr + (size_t)jj * vld), a);
+                acc[oo] = a;
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int oo = 0; oo < 8; oo++) {
+        const int o = threadIdx.x + oo * 128;
+        if (o < nout) part[((size_t)blockIdx.z * R + r) * (b.heads * b.vdim) + (size_t)h0 * b.vdim + o] = acc[oo];
     }
 }
 template <typename OT>
@@ -914,23 +1002,25 @@ __device__ __forceinline__ void sa_cp16(uint32_t dst, const void* src, bool vali
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
 
-template <int DP, int VP>
-__global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b, int S, const float* __restrict__ P, int ldp, const bf16* __restrict__ kc,
+template <int DP, int VP, int HPC>
+__global__ void __launch_bounds__(128 * HPC) k_sigattn_mma(PassTables t, AttnBranch b, int S, const float* __restrict__ P, int ldp, const bf16* __restrict__ kc,
                                                      const bf16* __restrict__ vc, bf16* __restrict__ out, int ld_out) {
     constexpr int LQ = DP + 8, LV = VP + 8;
     extern __shared__ __align__(16) unsigned char sa_raw[];
-    bf16* sq = reinterpret_cast<bf16*>(sa_raw);          // [64][LQ]
-    bf16* sk0 = sq + 64 * LQ;                           // [2][64][LQ]: key tiles, double-buffered
+    bf16* sq = reinterpret_cast<bf16*>(sa_raw);          // [HPC][64][LQ]: the CTA's query heads share one K/V head
+    bf16* sk0 = sq + HPC * 64 * LQ;                     // [2][64][LQ]: key tiles, double-buffered
     bf16* sv0 = sk0 + 2 * 64 * LQ;                      // [2][64][LV]
     int seg, q0;
     if (!sa_find_tile(t, S, blockIdx.x, seg, q0)) return;
-    const int h = blockIdx.y, g = h / (b.heads / b.kv_heads);
+    constexpr int NT = 128 * HPC;
+    const int hsub = (threadIdx.x >> 7);                 // which of the CTA's heads this warp works for
+    const int h = blockIdx.y * HPC + hsub, g = h / (b.heads / b.kv_heads);
     const int slot = t.seg_slot[seg], row0 = t.seg_row0[seg] + q0, nq = min(64, t.seg_len[seg] - q0);
     const int pos0 = t.row_pos[row0];                    // position of the tile's first row; row i sits at pos0 + i
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
-    for (int e = threadIdx.x; e < 64 * DP; e += 128) {
-        const int r = e / DP, i = e % DP;
-        sq[r * LQ + i] = __float2bfloat16_rn((r < nq && i < b.dim) ? P[(size_t)(row0 + r) * ldp + b.q_off + h * b.dim + i] : 0.0f);
+    const int warp = (threadIdx.x >> 5) & 3, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    for (int e = threadIdx.x; e < HPC * 64 * DP; e += NT) {
+        const int hh = e / (64 * DP), r = (e / DP) % 64, i = e % DP;
+        sq[(hh * 64 + r) * LQ + i] = __float2bfloat16_rn((r < nq && i < b.dim) ? P[(size_t)(row0 + r) * ldp + b.q_off + (blockIdx.y * HPC + hh) * b.dim + i] : 0.0f);
     }
     const float bias = b.pb ? b.pb[h] : 0.0f;
     const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
@@ -941,7 +1031,7 @@ __global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b,
 #pragma unroll
     for (int n = 0; n < VP / 8; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
     const int last = pos0 + nq - 1;                      // last key any row of the tile sees
-    const uint32_t sq_a = (uint32_t)__cvta_generic_to_shared(sq);
+    const uint32_t sq_a = (uint32_t)__cvta_generic_to_shared(sq + hsub * 64 * LQ);
     // tile j0 -> stage st: asynchronous 16-byte copies when the cache rows are 16-byte aligned, plain loads otherwise
     auto load_tile = [&](int st, int j0) {
         bf16* sk = sk0 + st * 64 * LQ;
@@ -949,22 +1039,22 @@ __global__ void __launch_bounds__(128) k_sigattn_mma(PassTables t, AttnBranch b,
         const int nk = min(64, last + 1 - j0);
         if (vec) {
             const uint32_t ka = (uint32_t)__cvta_generic_to_shared(sk), va = (uint32_t)__cvta_generic_to_shared(sv);
-            for (int e = threadIdx.x; e < 64 * (DP / 8); e += 128) {
+            for (int e = threadIdx.x; e < 64 * (DP / 8); e += NT) {
                 const int r = e / (DP / 8), c8 = (e % (DP / 8)) * 8;
                 const bool ok = r < nk && c8 < b.dim;
                 sa_cp16(ka + (uint32_t)((r * LQ + c8) * 2), ok ? (const void*)(kbase + (size_t)(j0 + r) * kld + c8) : (const void*)kbase, ok);
             }
-            for (int e = threadIdx.x; e < 64 * (VP / 8); e += 128) {
+            for (int e = threadIdx.x; e < 64 * (VP / 8); e += NT) {
                 const int r = e / (VP / 8), c8 = (e % (VP / 8)) * 8;
                 const bool ok = r < nk && c8 < b.vdim;
                 sa_cp16(va + (uint32_t)((r * LV + c8) * 2), ok ? (const void*)(vbase + (size_t)(j0 + r) * vld + c8) : (const void*)vbase, ok);
             }
         } else {
-            for (int e = threadIdx.x; e < 64 * DP; e += 128) {
+            for (int e = threadIdx.x; e < 64 * DP; e += NT) {
                 const int r = e / DP, i = e % DP;
                 sk[r * LQ + i] = (r < nk && i < b.dim) ? kbase[(size_t)(j0 + r) * kld + i] : __float2bfloat16_rn(0.0f);
             }
-            for (int e = threadIdx.x; e < 64 * VP; e += 128) {
+            for (int e = threadIdx.x; e < 64 * VP; e += NT) {
                 const int r = e / VP, i = e % VP;
                 sv[r * LV + i] = (r < nk && i < b.vdim) ? vbase[(size_t)(j0 + r) * vld + i] : __float2bfloat16_rn(0.0f);
             }
