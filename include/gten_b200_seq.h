@@ -97,8 +97,7 @@ int gtb_seq_last_logits(gtb_seq_t m, int seg, float* h_logits);
  * "tensor" (1, default: bf16 matrix products of >= "tensor_min_rows" rows on tcgen05; 0: SIMT kernels only),
  * "tensor_min_rows" (default 64), "graph" (1, default: gtb_seq_decode replays a CUDA graph per step),
  * "fused_attn" (1, default: tiled kernels of the mixers on prompt portions -- tensor-core sigmoid attention in bf16 mode, chunked
- * retention; 0: the row-at-a-time kernels), "fused_norm" (1, default: norm and input convolution in one kernel; 0: two kernels),
- * "group_decode" (1, default: decode-time attention scores a cached key once for all query heads of its group; 0: one CTA per head) */
+ * retention; 0: the row-at-a-time kernels), "fused_norm" (1, default: norm and input convolution in one kernel on passes of 32 rows or more; 0: two kernels) */
 int gtb_seq_set_option(gtb_seq_t m, const char* name, int value);
 int gtb_seq_read_capture(gtb_seq_t m, int run, int row, float* h_out);    /* [width] */
 /* self-test and timing of the bf16 tensor-core product on host data: C [M][N] = A [M][K] . W [N][K]^T (+ the incoming C when accumulate);

@@ -106,7 +106,6 @@ struct gtb_seq_model {
     bool use_graph = true;
     bool fused_attn = true;
     bool fused_norm = true;
-    bool group_decode = true;
     SeqGemmPlan* gp = nullptr;
     // decode graph
     cudaGraphExec_t graph = nullptr;
@@ -208,10 +207,8 @@ int launch_sigattn_mma(const PassTables& t, const AttnBranch& a, int S, int n_ti
 }
 int sigattn_mma(const PassTables& t, const AttnBranch& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, bf16* out, int ld_out) {
     const int dp = a.dim <= 32 ? 32 : a.dim <= 64 ? 64 : 128, vp = a.vdim <= 32 ? 32 : a.vdim <= 64 ? 64 : 128;
-    // two query heads of a group can share a CTA's K/V tiles (HPC = 2): measured equal to one head per CTA at 32 heads x 2048 rows, so off
-    const bool pair = false && (a.heads / a.kv_heads) % 2 == 0 && dp <= 64 && vp <= 64;
-#define SA_CASE(D, V) if (dp == D && vp == V) return pair ? launch_sigattn_mma<D, V, 2>(t, a, S, n_tiles, P, ldp, kc, vc, out, ld_out) \
-                                                              : launch_sigattn_mma<D, V, 1>(t, a, S, n_tiles, P, ldp, kc, vc, out, ld_out)
+    // (HPC = 2 -- two query heads of a group sharing a CTA's K/V tiles -- was measured equal to one head per CTA at 32 heads x 2048 rows)
+#define SA_CASE(D, V) if (dp == D && vp == V) return launch_sigattn_mma<D, V, 1>(t, a, S, n_tiles, P, ldp, kc, vc, out, ld_out)
     SA_CASE(32, 32); SA_CASE(32, 64); SA_CASE(32, 128); SA_CASE(64, 32); SA_CASE(64, 64); SA_CASE(64, 128); SA_CASE(128, 32); SA_CASE(128, 64); SA_CASE(128, 128);
 #undef SA_CASE
     return -1;
@@ -302,15 +299,9 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                     done = sigattn_mma(t, a, S, n_qtiles, m->P, l.n1, (const bf16*)run.kc[bi], (const bf16*)run.vc[bi], (bf16*)opC, l.kout_p);
                 if (done > 0) return done;
                 if (done < 0 && !portions && m->attn_splits > 1 && R <= SPLIT_MAX_ROWS) {
-                    const int hg = a.heads / a.kv_heads;
-                    const int hc = std::max(1, std::min(std::min(hg, 8), 1024 / a.vdim));     // query heads per CTA: at most 8 outputs per thread
-                    if (hg > 1 && hc > 1 && m->group_decode) {
-                        const int chunks = (hg + hc - 1) / hc;
-                        k_sigattn_split_group<OT><<<dim3(R, a.kv_heads * chunks, m->attn_splits), 128, (size_t)hc * (a.dim + 128) * sizeof(float), st>>>(
-                            t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], m->attn_part, R, hc);
-                    } else {
-                        k_sigattn_split<OT><<<dim3(R, a.heads, m->attn_splits), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], m->attn_part, R);
-                    }
+                    // (a group-major variant -- one CTA scoring a key for all query heads of its K/V head -- was measured slower at 32 heads
+                    // and 8 splits: 8x fewer CTAs on a latency-bound step)
+                    k_sigattn_split<OT><<<dim3(R, a.heads, m->attn_splits), 128, (a.dim + 128) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], m->attn_part, R);
                     GTB_LAUNCHED();
                     k_sigattn_join<OT><<<dim3(R, (a.heads * a.vdim + 255) / 256), 256, 0, st>>>(a, m->attn_part, R, m->attn_splits, opC, l.kout_p);
                     GTB_LAUNCHED();
@@ -891,7 +882,6 @@ int gtb_seq_set_option(gtb_seq_t m, const char* name, int value) {
     else if (n == "graph") m->use_graph = value != 0;
     else if (n == "fused_attn") m->fused_attn = value != 0;
     else if (n == "fused_norm") m->fused_norm = value != 0;
-    else if (n == "group_decode") m->group_decode = value != 0;
     else return gtb::fail(GTB_ERR_ARG, "unknown option '%s'", name);
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return GTB_OK;

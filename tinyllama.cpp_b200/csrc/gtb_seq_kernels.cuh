@@ -183,29 +183,18 @@ template <typename OT>
 __global__ void __launch_bounds__(256) k_norm_canon(PassTables t, const float* __restrict__ x, int width, float eps, const float* __restrict__ g, int taps,
                                                     const bf16* __restrict__ wa, const bf16* __restrict__ wb, const float* __restrict__ tail,
                                                     float* __restrict__ h, OT* __restrict__ out_a, OT* __restrict__ out_b, int ld_out) {
-    constexpr int MT = 8;                                   // taps <= MT (the host picks the two-kernel path otherwise)
-    __shared__ float red[8][MT];
-    __shared__ float inv[MT];
-    const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    __shared__ float inv[32];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
     const int s = t.row_seg[r], row0 = t.seg_row0[s], slot = t.seg_slot[s];
-    const int first = max(0, row0 - (r - (taps - 1)));      // taps [first, taps) lie inside the segment
-    float ss[MT];
-#pragma unroll
-    for (int j = 0; j < MT; j++) ss[j] = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x)
-#pragma unroll
-        for (int j = 0; j < MT; j++)
-            if (j >= first && j < taps) { const float v = x[(size_t)(r - (taps - 1) + j) * width + c]; ss[j] = fmaf(v, v, ss[j]); }
-#pragma unroll
-    for (int j = 0; j < MT; j++) {
-        const float v = warp_sum(ss[j]);
-        if (lane == 0) red[wid][j] = v;
-    }
-    __syncthreads();
-    if (threadIdx.x < taps) {
-        float v = 0.0f;
-        for (int w = 0; w < 8; w++) v += red[w][threadIdx.x];
-        inv[threadIdx.x] = (1.0f / sqrtf(v / (float)width + eps)) * g[0];
+    const float gain = g[0];
+    for (int j = wid; j < taps; j += nw) {
+        const int src = r - (taps - 1) + j;
+        if (src < row0) continue;                          // warp-uniform
+        const float* xr = x + (size_t)src * width;
+        float ss = 0.0f;
+        for (int c = lane; c < width; c += 32) { const float v = xr[c]; ss += v * v; }
+        ss = warp_sum(ss);
+        if (lane == 0) inv[j] = (1.0f / sqrtf(ss / (float)width + eps)) * gain;
     }
     __syncthreads();
     const float* tl = tail + (size_t)slot * (taps - 1) * width;
@@ -502,83 +491,6 @@ __global__ void __launch_bounds__(128) k_sigattn_split(PassTables t, AttnBranch 
         if (c < b.vdim) part[((size_t)blockIdx.z * R + r) * (b.heads * b.vdim) + h * b.vdim + c] = acc[cc];
     }
 }
-// The same split, group-major: a CTA takes a key range for up to 8 query heads that share one K/V head.  A thread reads its key's row
-// once and scores it against all of the group's queries; in the value phase a thread owns (4 heads x 1 channel)-like slices of the
-// group's outputs, so each cached value is read once per 4 heads instead of once per head.
-constexpr int SG_MAXH = 8;          // query heads per CTA
-template <typename OT>
-__global__ void __launch_bounds__(128) k_sigattn_split_group(PassTables t, AttnBranch b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc,
-                                                             const OT* __restrict__ vc, float* __restrict__ part, int R, int hc) {
-    extern __shared__ float sm[];
-    const int hg = b.heads / b.kv_heads;                 // query heads per K/V head
-    const int chunks = (hg + hc - 1) / hc;               // CTAs per group along y (hc heads each)
-    const int r = blockIdx.x, g = blockIdx.y / chunks, h0 = g * hg + (blockIdx.y % chunks) * hc, nh = min(hc, g * hg + hg - h0);
-    float* sq = sm;                                      // [hc][dim]
-    float* swt = sm + hc * b.dim;                        // [hc][128]
-    const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
-    const int per = ((pos + 1 + (int)gridDim.z - 1) / (int)gridDim.z + 127) / 128 * 128;
-    const int lo = blockIdx.z * per, hi = min(pos + 1, lo + per);
-    for (int e = threadIdx.x; e < nh * b.dim; e += 128) sq[e] = P[(size_t)r * ldp + b.q_off + (size_t)h0 * b.dim + e];
-    const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
-    const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
-    const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
-    const int nout = nh * b.vdim;                        // outputs of this CTA: (head, channel), at most 8 per thread
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; i++) acc[i] = 0.0f;
-    __syncthreads();
-    for (int j0 = lo; j0 < hi; j0 += 128) {
-        const int j = j0 + threadIdx.x;
-        float sc[SG_MAXH];
-#pragma unroll
-        for (int hh = 0; hh < SG_MAXH; hh++) sc[hh] = 0.0f;
-        if (j < hi) {
-            const OT* kr = kbase + (size_t)j * kld;
-            if (b.dim % 8 == 0) {                        // rows of the cache start on 16-byte boundaries then
-                for (int i = 0; i < b.dim; i += 8) {
-                    float kv[8];
-                    load8<OT>(kr + i, kv);
-#pragma unroll
-                    for (int hh = 0; hh < SG_MAXH; hh++)
-                        if (hh < nh) {
-#pragma unroll
-                            for (int q = 0; q < 8; q++) sc[hh] = fmaf(sq[hh * b.dim + i + q], kv[q], sc[hh]);
-                        }
-                }
-            } else {
-                for (int i = 0; i < b.dim; i++) {
-                    const float kv = ldf<OT>(kr + i);
-#pragma unroll
-                    for (int hh = 0; hh < SG_MAXH; hh++)
-                        if (hh < nh) sc[hh] = fmaf(sq[hh * b.dim + i], kv, sc[hh]);
-                }
-            }
-        }
-#pragma unroll
-        for (int hh = 0; hh < SG_MAXH; hh++)
-            if (hh < nh) swt[hh * 128 + threadIdx.x] = (j < hi) ? sigmoidf_(sc[hh] * b.scale + (b.pb ? b.pb[h0 + hh] : 0.0f)) : 0.0f;
-        __syncthreads();
-        const int nj = min(128, hi - j0);
-#pragma unroll
-        for (int oo = 0; oo < 8; oo++) {
-            const int o = threadIdx.x + oo * 128;
-            if (o < nout) {
-                const int hh = o / b.vdim, c = o % b.vdim;
-                float a = acc[oo];
-                const OT* vr = vbase + (size_t)j0 * vld + c;
-                const float* w = swt + hh * 128;
-                for (int jj = 0; jj < nj; jj++) a = fmaf(w[jj], ldf<OT>(vr + (size_t)jj * vld), a);
-                acc[oo] = a;
-            }
-        }
-        __syncthreads();
-    }
-#pragma unroll
-    for (int oo = 0; oo < 8; oo++) {
-        const int o = threadIdx.x + oo * 128;
-        if (o < nout) part[((size_t)blockIdx.z * R + r) * (b.heads * b.vdim) + (size_t)h0 * b.vdim + o] = acc[oo];
-    }
-}
 template <typename OT>
 __global__ void k_sigattn_join(AttnBranch b, const float* __restrict__ part, int R, int splits, OT* __restrict__ out, int ld_out) {
     const int r = blockIdx.x, n = b.heads * b.vdim;
@@ -857,11 +769,18 @@ __global__ void __launch_bounds__(256) k_ret_scan(PassTables t, RetBranch b, int
     float s0 = gs[e];
     float* u = U + (((size_t)first * b.heads + h) * b.dim) * b.vdim + e;
     const size_t stride = (size_t)b.heads * b.dim * b.vdim;
-    for (int c = 0; c < nchunk; c++, u += stride) {
-        const float add = *u;
-        *u = s0;
-        const int Lc = min(C, len - c * C);
-        s0 = fmaf(Lc == C ? gc : expf(lg * (float)Lc), s0, add);
+    // batches of 16 chunks: all of a batch's loads are issued before the dependent chain of multiply-adds starts
+    for (int c0 = 0; c0 < nchunk; c0 += 16) {
+        float add[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) add[i] = (c0 + i < nchunk) ? u[(size_t)(c0 + i) * stride] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; i++)
+            if (c0 + i < nchunk) {
+                u[(size_t)(c0 + i) * stride] = s0;
+                const int Lc = min(C, len - (c0 + i) * C);
+                s0 = fmaf(Lc == C ? gc : expf(lg * (float)Lc), s0, add[i]);
+            }
     }
     if (!t.slots[slot].stopped) gs[e] = s0;
 }
@@ -990,7 +909,7 @@ __device__ __forceinline__ float sa_sigmoid(float z) { return __fdividef(1.0f, 1
 __device__ __forceinline__ bool sa_find_tile(const PassTables& t, int S, int idx, int& seg, int& q0) {
     for (int s = 0; s < S; s++) {
         const int n = (t.seg_len[s] + 63) / 64;
-        if (idx < n) { seg = s; q0 = idx * 64; return true; }
+        if (idx < n) { seg = s; q0 = (n - 1 - idx) * 64; return true; }      // a segment's last tiles sweep the most keys: they start first
         idx -= n;
     }
     return false;
