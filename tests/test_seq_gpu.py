@@ -307,6 +307,23 @@ def test_tiled_mixer_kernels_on_portions(lib, mode, kw):
     assert rel(nxt, R.forward(cfg, W, np.append(a, 5))[0][-1:]) < TOL[mode]
 
 
+@pytest.mark.parametrize("kw", [
+    dict(vocab=101, width=72, ff=88, l_heads=6, l_kv=2, l_dim=12, l_vdim=20, r_heads=3, r_dim=24, r_vdim=16, rot_dims=12, taps=3),     # nothing a multiple of 32
+    dict(vocab=33, width=40, ff=24, l_heads=1, l_kv=1, l_dim=40, l_vdim=8, r_heads=1, r_dim=4, r_vdim=40, rot_dims=2, taps=9, n_layers=1),  # fewer outputs than a tile, long filter
+])
+def test_tensor_core_path_with_awkward_sizes(lib, kw):
+    """bfloat16 mode, portions of 64 rows and more (tcgen05 products, their row / column guards and unaligned epilogue stores)."""
+    cfg = small(**kw)
+    m, W = make(lib, cfg, "bfloat16", seed=67)
+    t = toks(120, 150, cfg["vocab"])
+    want, _ = R.forward(cfg, W, t)
+    got = np.concatenate([m.step([(0, t[:70])], range(70)), m.step([(0, t[70:])], range(80))])
+    assert rel(got, want) < TOL["bfloat16"]
+    m.set_option("tensor", 0)
+    simt = np.concatenate([m.step([(1, t[:70])], range(70)), m.step([(1, t[70:])], range(80))])
+    assert rel(got, simt) < 2e-2
+
+
 # ------------------------------------------------------------------ generation through the scheduler
 def oracle_greedy(cfg, W, prompt, n_new):
     t = list(prompt)
