@@ -191,7 +191,7 @@ RetChunk ret_chunk(const gtb_seq_branch& d) {
     r.vs = std::min(d.vdim, r.C);         // a state slice [dim][vs] must fit where the keys [dim][C] were
     const size_t dp = (d.dim + 3) & ~3, vsp = (r.vs + 3) & ~3;
     r.smem_kv = ((size_t)r.C * dp + (size_t)r.C * vsp) * sizeof(float);
-    r.smem_out = (2 * (size_t)r.C * d.dim + (size_t)r.C * vsp + (size_t)r.C * r.C) * sizeof(float);     // the incoming state reuses the keys' space
+    r.smem_out = (2 * (size_t)(r.C + 4) * d.dim + (size_t)r.C * vsp + (size_t)r.C * r.C) * sizeof(float);     // the incoming state reuses the keys' space
     r.ok = r.smem_out <= 200 * 1024;
     return r;
 }

@@ -796,22 +796,23 @@ __global__ void __launch_bounds__(256) k_ret_chunk_out(PassTables t, RetBranch b
     const int h = blockIdx.y, j0 = blockIdx.z * vs, nv = min(vs, b.vdim - j0);
     const int row0 = t.seg_row0[seg] + c * C, L = min(C, t.seg_len[seg] - c * C);
     const int vsp = (vs + 3) & ~3;
-    float* sq = sm;                       // [dim][C]
-    float* sk = sq + b.dim * C;           // [dim][C]; the same space holds s0 [dim][vsp] once the key products are done (vsp <= C)
-    float* sv = sk + b.dim * C;           // [C][vsp]
+    const int CP = C + 4;                 // row pitch of the transposed operands: float4 reads stay aligned, transposing stores hit 8 banks
+    float* sq = sm;                       // [dim][CP]
+    float* sk = sq + b.dim * CP;          // [dim][CP]; the same space holds s0 [dim][vsp] once the key products are done (vsp <= C)
+    float* sv = sk + b.dim * CP;          // [C][vsp]
     float* sa = sv + C * vsp;             // [C][C]
     float* s0 = sk;
     const float lg = logf(b.decay[h]);
-    for (int e = threadIdx.x; e < C * b.dim; e += blockDim.x) {
-        const int bb = e % C, i = e / C;
+    for (int e = threadIdx.x; e < C * b.dim; e += blockDim.x) {      // a warp reads 32 consecutive dims of one row
+        const int i = e % b.dim, bb = e / b.dim;
         float qv = 0.0f, kv = 0.0f;
         if (bb < L) {
             const float* p = P + (size_t)(row0 + bb) * ldp;
             qv = p[b.q_off + h * b.dim + i];
             kv = p[b.k_off + h * b.dim + i];
         }
-        sq[e] = qv;
-        sk[e] = kv;
+        sq[i * CP + bb] = qv;
+        sk[i * CP + bb] = kv;
     }
     for (int e = threadIdx.x; e < C * vsp; e += blockDim.x) {
         const int bb = e / vsp, j = e % vsp;
@@ -824,8 +825,8 @@ __global__ void __launch_bounds__(256) k_ret_chunk_out(PassTables t, RetBranch b
         float acc[4][4] = {};                           // [key][row]
         if (b4 <= a4 + 3 && a4 < L) {
             for (int i = 0; i < b.dim; i++) {
-                const float4 q4 = *reinterpret_cast<const float4*>(sq + i * C + a4);
-                const float4 k4 = *reinterpret_cast<const float4*>(sk + i * C + b4);
+                const float4 q4 = *reinterpret_cast<const float4*>(sq + i * CP + a4);
+                const float4 k4 = *reinterpret_cast<const float4*>(sk + i * CP + b4);
                 const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, kk[4] = {k4.x, k4.y, k4.z, k4.w};
 #pragma unroll
                 for (int y = 0; y < 4; y++)
@@ -864,7 +865,7 @@ __global__ void __launch_bounds__(256) k_ret_chunk_out(PassTables t, RetBranch b
                 for (int y = 0; y < 4; y++) intra[x][y] = fmaf(ww[x], vv[y], intra[x][y]);
         }
         for (int i = 0; i < b.dim; i++) {
-            const float4 q4 = *reinterpret_cast<const float4*>(sq + i * C + a4);
+            const float4 q4 = *reinterpret_cast<const float4*>(sq + i * CP + a4);
             const float4 z4 = *reinterpret_cast<const float4*>(s0 + i * vsp + j4);
             const float qq[4] = {q4.x, q4.y, q4.z, q4.w}, zz[4] = {z4.x, z4.y, z4.z, z4.w};
 #pragma unroll
