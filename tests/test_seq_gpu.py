@@ -413,3 +413,37 @@ def test_errors(lib):
     t.pop("l0.mix.right.g")
     with pytest.raises(lib.SeqError, match="right.g"):
         lib.SeqModel(d, lib.F32, 1, 16).load(t)
+
+
+def test_command_line_generation_and_trace_replay(lib, tmp_path):
+    """bin/generate and bin/trace_run on a checkpoint folder written by the family's own writer."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    from tinyllama_cpp_b200 import reninex
+    root = Path(__file__).resolve().parent.parent
+    cfg = small(vocab=64, width=64, n_layers=2, loop=(0, 1, 2))
+    desc = reninex.describe(cfg)
+    t = reninex.synth_tensors(desc, 71, gain=2.0)
+    reninex.write_checkpoint(tmp_path / "m", cfg, t)
+    W = {k: R.bf16_to_float(v) for k, v in t.items()}
+    p = toks(130, 17, 64)
+    out = subprocess.run([sys.executable, str(root / "bin" / "generate"), "--model", str(tmp_path / "m"), "--dtype", "float32", "--prompt",
+                          ",".join(map(str, p)), "--max-new", "6", "--chunk", "8"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    got = np.array([int(x) for x in out.stdout.strip().splitlines()[-1].split(",")])
+    want, margin = oracle_greedy(cfg, W, p, 6)
+    k = int(np.argmax(got != want)) if np.any(got != want) else 6
+    assert k == 6 or margin[k] < 1e-3
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": p[:9].tolist(), "want": [8, 2]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": p[9:].tolist(), "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "b", "tokens": p[:3].tolist(), "want": [2]}], "end": ["a", "b"]}]
+    tr = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(tmp_path / "m"), "--dtype", "float32", "--out", str(tmp_path / "o"), "--max-tokens", "64"],
+                        input="\n".join(json.dumps(x) for x in steps) + "\n", capture_output=True, text=True, timeout=300)
+    assert tr.returncode == 0, tr.stderr[-2000:]
+    assert [l for l in tr.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    lg = R.forward(cfg, W, p)[0]
+    a0 = np.fromfile(tmp_path / "o" / "0.f32", "<f4").reshape(2, 64)
+    assert rel(a0, lg[[8, 2]]) < TOL["float32"]                      # in the order asked for
+    assert not (tmp_path / "o" / "1.f32").exists()
+    assert rel(np.fromfile(tmp_path / "o" / "2.f32", "<f4").reshape(1, 64), lg[2:3]) < TOL["float32"]
