@@ -544,12 +544,12 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 m->retU_floats = std::max(m->retU_floats, chunks * d.heads * d.dim * d.vdim);
             }
     if (m->retU_floats) TRY(dalloc_t(m, &m->retU, m->retU_floats));
-    {   // key splits of decode-time attention: one CTA per ~256 keys of a full slot, at most 32
+    {   // key splits of decode-time attention: one CTA per 128 keys of a full slot, at most 32
         int hv = 0;
         for (const LayerW& l : m->L)
             for (int bi = 0; bi < l.d.n_branches; bi++)
                 if (l.br[bi].d.kind == GTB_MIX_SIGMOID_ATTN) hv = std::max(hv, l.br[bi].d.heads * l.br[bi].d.vdim);
-        m->attn_splits = std::max(1, std::min(32, c.max_ctx / 256));
+        m->attn_splits = std::max(1, std::min(32, c.max_ctx / 128));
         if (hv > 0 && m->attn_splits > 1) TRY(dalloc_t(m, &m->attn_part, (size_t)m->attn_splits * SPLIT_MAX_ROWS * hv));
     }
     TRY(dalloc_t(m, &m->logits, R * c.vocab));

@@ -462,6 +462,7 @@ __global__ void __launch_bounds__(128) k_sigattn_split(PassTables t, AttnBranch 
     const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
     const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    const int kg = b.vdim <= 32 ? 4 : b.vdim <= 64 ? 2 : 1, cw = 128 / kg;      // key groups of the value phase and their width
     const bool kvec = b.dim % 8 == 0;            // rows of the cache start on 16-byte boundaries then
     __syncthreads();
     for (int j0 = lo; j0 < hi; j0 += blockDim.x) {
@@ -473,17 +474,39 @@ __global__ void __launch_bounds__(128) k_sigattn_split(PassTables t, AttnBranch 
         swt[threadIdx.x] = w;
         __syncthreads();
         const int nj = min((int)blockDim.x, hi - j0);
-#pragma unroll
-        for (int cc = 0; cc < 4; cc++) {
-            const int c = threadIdx.x + cc * blockDim.x;
+        if (kg > 1) {                                    // narrow heads: kg thread groups take every kg-th key of the tile
+            const int c = threadIdx.x % cw, grp = threadIdx.x / cw;
             if (c < b.vdim) {
-                float a = acc[cc];
+                float a = acc[0];
                 const OT* vr = vbase + (size_t)j0 * vld + c;
-                for (int jj = 0; jj < nj; jj++) a = fmaf(swt[jj], ldf<OT>(vr + (size_t)jj * vld), a);
-                acc[cc] = a;
+#pragma unroll 4
+                for (int jj = grp; jj < nj; jj += kg) a = fmaf(swt[jj], ldf<OT>(vr + (size_t)jj * vld), a);
+                acc[0] = a;
+            }
+        } else {
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) {
+                const int c = threadIdx.x + cc * blockDim.x;
+                if (c < b.vdim) {
+                    float a = acc[cc];
+                    const OT* vr = vbase + (size_t)j0 * vld + c;
+                    for (int jj = 0; jj < nj; jj++) a = fmaf(swt[jj], ldf<OT>(vr + (size_t)jj * vld), a);
+                    acc[cc] = a;
+                }
             }
         }
         __syncthreads();
+    }
+    if (kg > 1) {                                        // the groups' partial sums meet in shared memory, group 0 stores
+        swt[threadIdx.x] = acc[0];
+        __syncthreads();
+        const int c = threadIdx.x;
+        if (c < b.vdim) {
+            float a = 0.0f;
+            for (int q = 0; q < kg; q++) a += swt[q * cw + c];
+            part[((size_t)blockIdx.z * R + r) * (b.heads * b.vdim) + h * b.vdim + c] = a;
+        }
+        return;
     }
 #pragma unroll
     for (int cc = 0; cc < 4; cc++) {
