@@ -438,10 +438,13 @@ def test_command_line_generation_and_trace_replay(lib, tmp_path):
     steps = [{"step": 0, "entries": [{"id": "a", "tokens": p[:9].tolist(), "want": [8, 2]}], "end": []},
              {"step": 1, "entries": [{"id": "a", "tokens": p[9:].tolist(), "want": []}], "end": []},
              {"step": 2, "entries": [{"id": "b", "tokens": p[:3].tolist(), "want": [2]}], "end": ["a", "b"]}]
+    # six more requests that are never ended, on four slots: the one idle longest gives way
+    steps += [{"step": 3 + i, "entries": [{"id": f"c{i}", "tokens": p[:4 + i].tolist(), "want": [3 + i]}], "end": []} for i in range(6)]
     tr = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(tmp_path / "m"), "--dtype", "float32", "--out", str(tmp_path / "o"), "--max-tokens", "64"],
                         input="\n".join(json.dumps(x) for x in steps) + "\n", capture_output=True, text=True, timeout=300)
     assert tr.returncode == 0, tr.stderr[-2000:]
-    assert [l for l in tr.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+    assert [l for l in tr.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(9)]
+    assert rel(np.fromfile(tmp_path / "o" / "8.f32", "<f4").reshape(1, 64), R.forward(cfg, W, p[:9])[0][8:9]) < TOL["float32"]
     lg = R.forward(cfg, W, p)[0]
     a0 = np.fromfile(tmp_path / "o" / "0.f32", "<f4").reshape(2, 64)
     assert rel(a0, lg[[8, 2]]) < TOL["float32"]                      # in the order asked for
