@@ -1,10 +1,12 @@
 /* gten_b200_seq.h -- C-ABI of libgten_b200_seq.so: layer-list sequence models on one B200 (sm_100a).
  *
  * The hot path of include/gten_b200.h is one fixed graph (TinyLlama) with the reference's quantised arithmetic.  This
- * library runs models that are DESCRIBED: a list of layers, each a parallel block (one norm, a token mixer made of
+ * library runs models that are DESCRIBED: a list of layers, each either a parallel block (one norm, a token mixer made of
  * weighted branches, an optional gated feed-forward, both fed through a short causal convolution of the normalised
- * stream), an optional weight-shared loop over a range of layers, an optional hashed bigram embedding.  Weights are
- * bfloat16; the compute mode is bfloat16 operands with fp32 accumulation (tensor cores) or true fp32.
+ * stream) or a pair of sequential sublayers that read the stream itself and are normalised on their way back into it
+ * (mixer, then a dense or routed feed-forward); an optional weight-shared loop over a range of layers, an optional hashed
+ * bigram embedding, an optional embedding scale.  Weights are bfloat16; the compute mode is bfloat16 operands with fp32
+ * accumulation (tensor cores) or true fp32.
  *
  * It shares the context, the stream, the allocator and the error convention with gten_b200.h (the gtb_* calls of that
  * header are exported by this library as well): 0 on success, a message in gtb_last_error() otherwise.
@@ -23,7 +25,10 @@ extern "C" {
 #endif
 
 enum { GTB_SEQ_BF16 = 0, GTB_SEQ_F32 = 1 };                       /* compute mode */
-enum { GTB_MIX_SIGMOID_ATTN = 1, GTB_MIX_RETENTION = 2 };         /* branch kinds of a token mixer */
+enum { GTB_MIX_SIGMOID_ATTN = 1, GTB_MIX_RETENTION = 2, GTB_MIX_MINGRU = 3, GTB_MIX_SOFTMAX_ATTN = 4 };   /* branch kinds of a token mixer */
+enum { GTB_BLOCK_PARALLEL = 0, GTB_BLOCK_POSTNORM = 1 };          /* layer styles */
+enum { GTB_FF_GEGLU = 0, GTB_FF_POLYNORM = 1, GTB_FF_EXPERTS = 2 };   /* feed-forward kinds */
+enum { GTB_ROT_HALVES = 0, GTB_ROT_INTERLEAVED = 1 };             /* which entries a rotary pair takes: (i, i + dims/2) or (2i, 2i + 1) */
 
 /* One branch of a token mixer.  Tensors of branch b of layer i are "l<i>.mix.<name>.{q,k,v,o,...}".
  *  GTB_MIX_SIGMOID_ATTN: causal attention over the slot's K/V cache, `heads` query heads sharing `kv_heads` key/value
@@ -31,7 +36,18 @@ enum { GTB_MIX_SIGMOID_ATTN = 1, GTB_MIX_RETENTION = 2 };         /* branch kind
  *    qk_norm: q and k scaled to unit RMS per head (eps of the model).  Tensors q, k, v, pb, o.
  *  GTB_MIX_RETENTION: S <- decay[head] * S + k v^T, o = S^T q per head (fp32 state per slot); rotary positions on the
  *    first rot_dims dimensions of q and k (pairs i, i + rot_dims/2, angle pos * rot_base^(-2i/rot_dims)); k multiplied
- *    by `scale` after rotation; out_norm: o scaled to unit RMS per head; gated: o *= silu(g h).  Tensors q, k, v, g, o. */
+ *    by `scale` after rotation; out_norm: o scaled to unit RMS per head; gated: o *= silu(g h).  Tensors q, k, v, g, o.
+ *  GTB_MIX_MINGRU: S <- (1 - z) S + z c per channel (fp32 state per slot, `dim` channels, heads = 1), z = logistic(z h + z.b),
+ *    c = u + 1/2 for u >= 0 and logistic(u) below with u = x h + x.b; output o (S * silu(g h)).  Tensors z, z.b, x, x.b, g, o.
+ *  GTB_MIX_SOFTMAX_ATTN: softmax attention over the slot's K/V cache with grouped heads.  qk_norm 2: q and k to unit RMS per head
+ *    times the weight q.norm / k.norm [dim] (1: unit RMS only); rotary positions on the first rot_dims entries in rot_layout, with
+ *    frequencies rot_base^(-2i/rot_dims) rescaled when rot_factor > 0 (wavelengths above rot_original / rot_low divided by
+ *    rot_factor, those below rot_original / rot_high kept, a linear blend in rot_original / wavelength between); score =
+ *    scale q.k, then softcap * tanh(score / softcap) when softcap > 0; window > 0: position i sees tokens i - window < j <= i and,
+ *    when pool > 0, one mean key / mean value for every block [b pool, (b + 1) pool) that ends at or before i - window; sink: the
+ *    denominator also holds exp(sink[head]); gated 2: output times logistic(g h) (1: silu) before the out projection; kv_from >= 0:
+ *    no k / v tensors, keys and values are those of layer kv_from's cache (an earlier GTB_MIX_SOFTMAX_ATTN layer with the same
+ *    kv_heads, dim, vdim).  Tensors q, k, v, q.norm, k.norm, sink, g, o. */
 typedef struct {
     int kind;
     char name[16];
@@ -43,12 +59,26 @@ typedef struct {
     int out_norm, gated;
     float out_scale;                 /* weight of this branch in the mixer's sum */
     const float* decay;              /* [heads], host; copied */
+    int rot_layout;                  /* GTB_ROT_* */
+    float rot_factor, rot_low, rot_high, rot_original;     /* rot_factor = 0: plain frequencies */
+    float softcap;                   /* 0: none */
+    int window, pool;                /* 0: every earlier token / no pooled blocks */
+    int sink;                        /* 1: learned per-head sink in the softmax denominator */
+    int kv_from;                     /* -1: own keys and values */
 } gtb_seq_branch;
 
 typedef struct {
     int n_branches;                  /* 1 or 2 */
     gtb_seq_branch branch[2];
-    int ff;                          /* 0: no feed-forward; else W_down(gelu_tanh(W_gate h) * (W_up h)) */
+    int ff;                          /* 0: no feed-forward; else its inner width (of one expert for GTB_FF_EXPERTS) */
+    int style;                       /* GTB_BLOCK_PARALLEL: x += mixer(h) + ff(h), h = gain-norm(x) (+ convolutions);
+                                      * GTB_BLOCK_POSTNORM: x += norm1(mixer(x)); x += norm2(ff(x)), norms with weight vectors (1 + w),
+                                      * one branch, out_scale unused */
+    int ff_kind;                     /* GTB_FF_GEGLU: down(gelu_tanh(gate h) * (up h)); GTB_FF_POLYNORM: down(a N(z) + b N(z^2) + c N(z^3) + e),
+                                      * z = up h, N = unit RMS over the ff values, (a, b, c, e) = tensor mlp.act; GTB_FF_EXPERTS: router outputs
+                                      * 0 .. experts-1 are experts e<i>.down(relu(e<i>.up h)^2), the `identity` outputs after them return h;
+                                      * s = softmax(router h), the `top` largest s + correction are chosen and weighted with their s */
+    int experts, top, identity;
 } gtb_seq_layer;
 
 typedef struct {
@@ -60,6 +90,8 @@ typedef struct {
     int mode;                        /* GTB_SEQ_BF16 / GTB_SEQ_F32 */
     int n_slots, max_ctx;            /* sequences held at once; positions per slot */
     int max_rows;                    /* rows per pass over the weights (longer steps are cut into passes); 0: default */
+    float embed_scale;               /* embedding rows are multiplied by this (0 counts as 1) */
+    int final_norm;                  /* 0: one gain; 1: weight vector stored around zero (1 + w) */
 } gtb_seq_config;
 
 typedef struct gtb_seq_model* gtb_seq_t;
@@ -96,8 +128,9 @@ int gtb_seq_last_logits(gtb_seq_t m, int seg, float* h_logits);
 /* options: "capture" (1: the residual stream after every layer run of the last pass is kept for gtb_seq_read_capture),
  * "tensor" (1, default: bf16 matrix products of >= "tensor_min_rows" rows on tcgen05; 0: SIMT kernels only),
  * "tensor_min_rows" (default 64), "graph" (1, default: gtb_seq_decode replays a CUDA graph per step),
- * "fused_attn" (1, default: tiled kernels of the mixers on prompt portions -- tensor-core sigmoid attention in bf16 mode, chunked
- * retention; 0: the row-at-a-time kernels), "fused_norm" (1, default: norm and input convolution in one kernel on passes of 32 rows or more; 0: two kernels) */
+ * "fused_attn" (1, default: tiled kernels of the mixers on prompt portions -- tensor-core attention in bf16 mode, chunked
+ * retention and minGRU; 0: the row-at-a-time kernels), "grouped_experts" (1, default: rows sorted by expert and multiplied as groups
+ * on passes of tensor_min_rows rows or more; 0: one weight stream per row and choice), "fused_norm" (1, default: norm and input convolution in one kernel on passes of 32 rows or more; 0: two kernels) */
 int gtb_seq_set_option(gtb_seq_t m, const char* name, int value);
 int gtb_seq_read_capture(gtb_seq_t m, int run, int row, float* h_out);    /* [width] */
 /* self-test and timing of the bf16 tensor-core product on host data: C [M][N] = A [M][K] . W [N][K]^T (+ the incoming C when accumulate);

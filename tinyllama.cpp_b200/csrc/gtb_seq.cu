@@ -7,6 +7,10 @@
 //    projection are concatenated along K, so the residual update is ONE product that accumulates into the fp32 stream.
 //  * every operand / weight row is zero-padded to a multiple of 64 elements (one tensor-core k-block, 16-byte aligned rows).
 //  * a looped layer has one set of weights and one set of state (cache, recurrent state, conv history) per pass: a "run".
+//  * post-norm layers (GTB_BLOCK_POSTNORM) run their two sublayers one after the other: [branch projections] <- x, mixer, out
+//    projection into a fresh block Y, x += norm1(Y); then the feed-forward the same way.  Experts' up matrices are stacked along N
+//    ([experts * ff][width]) and their down matrices are stored one after the other ([experts][width][ff padded to 64]), which is what
+//    both the per-row kernels and the grouped product read.
 #include <math.h>
 #include <string.h>
 
@@ -19,6 +23,7 @@
 #include "gtb_sample.cuh"
 #include "gtb_seq_gemm.h"
 #include "gtb_seq_kernels.cuh"
+#include "gtb_seq_mixers.cuh"
 
 using namespace gtb;
 using namespace gtb::seq;
@@ -46,6 +51,7 @@ struct BranchW {
     float* d_pb = nullptr;
     float* d_decay = nullptr;
     float* d_inv_freq = nullptr;
+    float *d_qnorm = nullptr, *d_knorm = nullptr, *d_sink = nullptr;
 };
 
 struct LayerW {
@@ -57,6 +63,13 @@ struct LayerW {
     bf16 *w_mix = nullptr, *w_gu = nullptr, *w_out = nullptr, *canon_a = nullptr, *canon_b = nullptr;
     float* d_gain = nullptr;
     bool gu_inter = false;     // gate and up rows interleaved in groups of 32 (what the fused tensor-core epilogue reads)
+    // post-norm style
+    float *d_bias = nullptr;   // bias of the fused branch projection [n1] (minGRU), or null
+    float *norm1 = nullptr, *norm2 = nullptr;
+    bf16 *w_up = nullptr, *w_down = nullptr, *w_router = nullptr;
+    float *d_act = nullptr, *d_corr = nullptr;
+    int kfp = 0;               // inner width of the feed-forward (of one expert), padded to 64
+    int n_out = 0;             // router outputs: experts + identity
 };
 
 struct Run {
@@ -65,6 +78,8 @@ struct Run {
     void *kc[2] = {nullptr, nullptr}, *vc[2] = {nullptr, nullptr};
     float* state[2] = {nullptr, nullptr};
     float* tail = nullptr;
+    float *pk = nullptr, *pv = nullptr;     // mean key / value of every completed block of `pool` tokens [n_slots][max_blocks][kv_heads * dim|vdim]
+    int max_blocks = 0;
 };
 
 }  // namespace
@@ -89,6 +104,14 @@ struct gtb_seq_model {
     int attn_splits = 1;
     float* retU = nullptr;                       // chunked retention: per-chunk contributions / states [chunks][heads][dim][vdim]
     size_t retU_floats = 0;
+    float* gruAB = nullptr;                      // chunked minGRU: per-chunk maps [chunks][2][width]
+    size_t gruAB_floats = 0;
+    float* rl = nullptr;                         // router logits [max_rows][n_out_max]
+    int* sel_idx = nullptr;                      // chosen router outputs [max_rows][top_max]
+    float* sel_w = nullptr;
+    void* act = nullptr;                         // expert activations [max_rows * top_max][kfp_max]
+    int n_out_max = 0, top_max = 0, kfp_max = 0, g_cols = 0;
+    bool grouped_experts = true;
     float* cap = nullptr;                        // [runs][max_rows][width]
     bool capture = false;
     int cap_rows = 0;
@@ -137,6 +160,9 @@ void want_vector(gtb_seq_model* m, const std::string& name, float* dst, int rows
 }
 
 size_t osz(const gtb_seq_model* m) { return m->cfg.mode == GTB_SEQ_F32 ? 4 : 2; }
+// fp32 values of recurrent state one slot holds for a branch
+size_t state_floats(const gtb_seq_branch& d) { return d.kind == GTB_MIX_MINGRU ? (size_t)d.dim : (size_t)d.heads * d.dim * d.vdim; }
+constexpr int GRU_CHUNK = 64;               // rows per chunk of the chunked minGRU scan
 
 // C = (acc ? C : 0) + bias + A . W^T on the library stream; picks the tensor-core kernel, the few-row kernel or the SIMT tile kernel
 template <typename OT>
@@ -227,6 +253,100 @@ RetLaunch ret_launch(const gtb_seq_branch& d) {
     return r;
 }
 
+GruBranch gru_args(const BranchW& b) {
+    GruBranch a{};
+    a.width = b.d.dim; a.z_off = b.q_off; a.x_off = b.k_off; a.g_off = b.g_off; a.a_off = b.a_off;
+    return a;
+}
+SoftAttn soft_args(const gtb_seq_model* m, const BranchW& b, const Run& run) {
+    SoftAttn a{};
+    a.heads = b.d.heads; a.kv_heads = b.d.kv_heads; a.dim = b.d.dim; a.vdim = b.d.vdim;
+    a.scale = b.d.scale; a.eps = m->cfg.eps; a.softcap = b.d.softcap;
+    a.qk_norm = b.d.qk_norm; a.q_norm = b.d_qnorm; a.k_norm = b.d_knorm;
+    a.rot_dims = b.d.rot_dims; a.rot_layout = b.d.rot_layout; a.inv_freq = b.d_inv_freq;
+    a.window = b.d.window; a.pool = (b.d.window > 0) ? b.d.pool : 0; a.sink = b.d_sink; a.gate = b.d.gated;
+    a.q_off = b.q_off; a.k_off = b.k_off; a.v_off = b.v_off; a.g_off = b.g_off; a.a_off = b.a_off;
+    a.own_kv = b.d.kv_from < 0; a.max_ctx = m->cfg.max_ctx; a.max_blocks = run.max_blocks;
+    return a;
+}
+
+// One layer of the post-norm style on R rows: x += norm1(mixer(x)); x += norm2(ff(x)).  opA holds the stream as a product operand
+// when x_in_opA (the residual update of the previous sublayer wrote it) and always does on return.
+template <typename OT>
+int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, const LayerW& l, bool portions, const int* seg_lens, bool x_in_opA) {
+    cudaStream_t st = ctx().stream;
+    const gtb_seq_config& c = m->cfg;
+    const int W = c.width, wp = m->wp;
+    OT *opA = (OT*)m->opA, *opC = (OT*)m->opC;
+    if (!x_in_opA) {
+        k_copy_operand<OT><<<R, 256, 0, st>>>(m->x, W, opA, (OT*)nullptr, wp);
+        GTB_LAUNCHED();
+    }
+    int rc = product<OT>(m, opA, wp, l.w_mix, wp, m->P, l.n1, R, l.n1, wp, l.d_bias, 0);
+    if (rc) return rc;
+    const BranchW& b = l.br[0];
+    if (b.d.kind == GTB_MIX_MINGRU) {
+        const GruBranch a = gru_args(b);
+        const int cb = (a.width + 127) / 128;
+        if (portions) {
+            int n_chunks = 0;
+            for (int s = 0; s < S; s++) n_chunks += (seg_lens[s] + GRU_CHUNK - 1) / GRU_CHUNK;
+            if ((size_t)n_chunks * 2 * a.width > m->gruAB_floats) return gtb::fail(GTB_ERR_STATE, "chunk workspace too small");
+            k_mingru_chunk<<<dim3(n_chunks, cb), 128, 0, st>>>(t, a, m->P, l.n1, S, GRU_CHUNK, m->gruAB);
+            GTB_LAUNCHED();
+            k_mingru_chunk_out<OT><<<dim3(n_chunks, cb), 128, 0, st>>>(t, a, m->P, l.n1, S, GRU_CHUNK, m->gruAB, run.state[0], opC, l.kout_p);
+            GTB_LAUNCHED();
+            k_mingru_store<<<dim3(S, cb), 128, 0, st>>>(t, a, S, GRU_CHUNK, m->gruAB, run.state[0]);
+            GTB_LAUNCHED();
+        } else {
+            k_mingru<OT><<<dim3(S, cb), 128, 0, st>>>(t, a, m->P, l.n1, run.state[0], opC, l.kout_p);
+            GTB_LAUNCHED();
+        }
+    } else {
+        const SoftAttn a = soft_args(m, b, run);
+        k_sattn_prep<OT><<<dim3(R, (a.heads + 2 * a.kv_heads + 3) / 4), 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[0], (OT*)run.vc[0]);
+        GTB_LAUNCHED();
+        if (a.pool > 0) {
+            k_pool_update<OT><<<R, 128, 0, st>>>(t, a, (const OT*)run.kc[0], (const OT*)run.vc[0], run.pk, run.pv);
+            GTB_LAUNCHED();
+        }
+        k_sattn<OT><<<dim3(R, a.heads), 128, (a.dim + 128 + 33) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[0], (const OT*)run.vc[0], run.pk, run.pv, opC, l.kout_p);
+        GTB_LAUNCHED();
+    }
+    rc = product<OT>(m, opC, l.kout_p, l.w_out, l.kout_p, m->Y, W, R, W, l.kout_p, nullptr, 0);
+    if (rc) return rc;
+    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm1, nullptr, nullptr, 0, 0, m->x, opA, wp);
+    GTB_LAUNCHED();
+    if (l.ff == 0) return GTB_OK;
+    if (l.d.ff_kind == GTB_FF_POLYNORM) {
+        rc = product<OT>(m, opA, wp, l.w_up, wp, m->G, l.ff, R, l.ff, wp, nullptr, 0);
+        if (rc) return rc;
+        k_polynorm<OT><<<R, 256, 0, st>>>(m->G, l.ff, l.ff, c.eps, l.d_act, opC, l.kfp);
+        GTB_LAUNCHED();
+        rc = product<OT>(m, opC, l.kfp, l.w_down, l.kfp, m->Y, W, R, W, l.kfp, nullptr, 0);
+        if (rc) return rc;
+        k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, nullptr, nullptr, 0, 0, m->x, opA, wp);
+        GTB_LAUNCHED();
+        return GTB_OK;
+    }
+    const int E = l.d.experts, top = l.d.top;
+    rc = product<OT>(m, opA, wp, l.w_router, wp, m->rl, l.n_out, R, l.n_out, wp, nullptr, 0);
+    if (rc) return rc;
+    k_moe_route<<<R, 32, 2 * l.n_out * sizeof(float), st>>>(m->rl, l.n_out, l.n_out, l.d_corr, top, m->sel_idx, m->sel_w);
+    GTB_LAUNCHED();
+    if (E > 0) {
+        k_moe_up_rows<OT><<<dim3(R * top, std::max(1, std::min(8, (l.kfp + 7) / 8))), 256, 0, st>>>(opA, wp, wp, l.w_up, wp, l.ff, l.kfp, E, top, m->sel_idx, m->sel_w, (OT*)m->act);
+        GTB_LAUNCHED();
+        k_moe_down_rows<OT><<<dim3(R, std::max(1, std::min(16, (W + 7) / 8))), 256, 0, st>>>((const OT*)m->act, l.kfp, l.w_down, W, E, top, m->sel_idx, m->Y, W);
+        GTB_LAUNCHED();
+    } else {
+        GTB_CUDA(cudaMemsetAsync(m->Y, 0, (size_t)R * W * sizeof(float), st));
+    }
+    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, m->x, opA, wp);
+    GTB_LAUNCHED();
+    return GTB_OK;
+}
+
 // the launch sequence of one pass: R rows of S segments whose tables are already on the device
 template <typename OT>
 int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pending, int n_want, const int* d_want, const int* seg_lens = nullptr) {
@@ -240,11 +360,25 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
     if (portions) for (int s = 0; s < S; s++) n_qtiles += (seg_lens[s] + 63) / 64;
     k_plan<<<(R + 127) / 128, 128, 0, st>>>(t, R, from_pending ? 1 : 0);
     GTB_LAUNCHED();
-    k_embed<<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, m->x, c.loop_times > 0 ? m->x0 : nullptr);
+    k_embed<<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, c.embed_scale != 0.0f ? c.embed_scale : 1.0f,
+                               m->x, c.loop_times > 0 ? m->x0 : nullptr);
     GTB_LAUNCHED();
+    bool x_in_opA = false;
     for (size_t u = 0; u < m->runs.size(); u++) {
         const Run& run = m->runs[u];
         const LayerW& l = m->L[run.layer];
+        if (l.d.style == GTB_BLOCK_POSTNORM) {
+            if (run.enters_pass) return gtb::fail(GTB_ERR_STATE, "a post-norm layer cannot open a loop pass");
+            int rc = run_postnorm_layer<OT>(m, t, R, S, run, l, portions, seg_lens, x_in_opA);
+            if (rc) return rc;
+            x_in_opA = true;
+            if (m->capture) {
+                GTB_CUDA(cudaMemcpyAsync(m->cap + u * (size_t)m->max_rows * W, m->x, (size_t)R * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
+                m->cap_rows = R;
+            }
+            continue;
+        }
+        x_in_opA = false;
         if (run.enters_pass) {
             k_concat2<OT><<<R, 256, 0, st>>>(m->x, m->x0, W, opL, pad64(2 * W));
             GTB_LAUNCHED();
@@ -355,7 +489,8 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
         }
     }
     if (n_want > 0) {
-        k_rmsnorm_scalar<OT><<<n_want, 256, 0, st>>>(m->x, W, c.eps, m->final_gain, d_want, opH, wp);
+        if (c.final_norm) k_rmsnorm_weight<OT><<<n_want, 256, 0, st>>>(m->x, W, c.eps, m->final_gain, 1, d_want, opH, wp);
+        else k_rmsnorm_scalar<OT><<<n_want, 256, 0, st>>>(m->x, W, c.eps, m->final_gain, d_want, opH, wp);
         GTB_LAUNCHED();
         int rc = product<OT>(m, opH, wp, m->head, wp, m->logits, c.vocab, n_want, c.vocab, wp, nullptr, 0);
         if (rc) return rc;
@@ -403,8 +538,10 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     }
     TRY(dalloc_t(m, &m->head, (size_t)c.vocab * wp));
     want_matrix(m, "head", m->head, c.vocab, W, wp);
-    TRY(dalloc_t(m, &m->final_gain, 1));
-    want_vector(m, "final.norm", m->final_gain, 0, 0, true);
+    REQ(c.final_norm == 0 || c.final_norm == 1);
+    TRY(dalloc_t(m, &m->final_gain, c.final_norm ? W : 1));
+    if (c.final_norm) want_vector(m, "final.norm", m->final_gain, W, 0);
+    else want_vector(m, "final.norm", m->final_gain, 0, 0, true);
     if (c.loop_times > 0) {
         TRY(dalloc_t(m, &m->loop_in, (size_t)W * pad64(2 * W)));
         want_matrix(m, "loop.in", m->loop_in, W, 2 * W, pad64(2 * W));
@@ -415,8 +552,11 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     for (int i = 0; i < c.n_layers; i++) {
         LayerW& l = m->L[i];
         l.d = layers[i];
-        REQ(l.d.n_branches >= 1 && l.d.n_branches <= 2);
+        const bool post = l.d.style == GTB_BLOCK_POSTNORM;
+        REQ(l.d.style == GTB_BLOCK_PARALLEL || l.d.style == GTB_BLOCK_POSTNORM);
+        REQ(l.d.n_branches >= 1 && l.d.n_branches <= (post ? 1 : 2));
         REQ(l.d.ff >= 0);
+        REQ(post ? (l.d.ff == 0 || l.d.ff_kind == GTB_FF_POLYNORM || l.d.ff_kind == GTB_FF_EXPERTS) : l.d.ff_kind == GTB_FF_GEGLU);
         l.ff = l.d.ff;
         const std::string lp = "l" + std::to_string(i) + ".";
         int n1 = 0, ko = 0;
@@ -424,12 +564,49 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
             BranchW& b = l.br[bi];
             b.d = l.d.branch[bi];
             gtb_seq_branch& d = b.d;
-            REQ(d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_RETENTION);
+            REQ(post ? (d.kind == GTB_MIX_MINGRU || d.kind == GTB_MIX_SOFTMAX_ATTN) : (d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_RETENTION));
+            if (d.kind == GTB_MIX_MINGRU) {
+                REQ(d.dim > 0);
+                d.heads = d.kv_heads = 1; d.vdim = d.dim; d.rot_dims = 0;
+                b.q_off = n1; b.k_off = n1 + d.dim; b.g_off = n1 + 2 * d.dim; n1 += 3 * d.dim;      // update gate | candidate | output gate
+                b.a_off = ko; ko += d.dim;
+                continue;
+            }
             REQ(d.heads > 0 && d.dim > 0 && d.vdim > 0 && d.dim <= 1024 && d.vdim <= 512);
             if (d.kind == GTB_MIX_RETENTION) d.kv_heads = d.heads;
             REQ(d.kv_heads > 0 && d.heads % d.kv_heads == 0);
             REQ(d.rot_dims >= 0 && d.rot_dims <= d.dim && d.rot_dims % 2 == 0);
             b.kq = d.heads * d.dim; b.kk = d.kv_heads * d.dim; b.kv = d.kv_heads * d.vdim;
+            if (d.kind == GTB_MIX_SOFTMAX_ATTN) {
+                REQ(d.qk_norm >= 0 && d.qk_norm <= 2 && d.gated >= 0 && d.gated <= 2 && d.window >= 0 && d.pool >= 0 && d.softcap >= 0.0f);
+                REQ(d.kv_from < i);
+                if (d.kv_from >= 0) {
+                    REQ(c.loop_times == 0);
+                    const LayerW& src = m->L[d.kv_from];
+                    REQ(src.d.style == GTB_BLOCK_POSTNORM && src.br[0].d.kind == GTB_MIX_SOFTMAX_ATTN && src.br[0].d.kv_from < 0);
+                    REQ(src.br[0].d.kv_heads == d.kv_heads && src.br[0].d.dim == d.dim && src.br[0].d.vdim == d.vdim);
+                } else d.kv_from = -1;
+                b.q_off = n1; n1 += b.kq;
+                if (d.kv_from < 0) { b.k_off = n1; n1 += b.kk; b.v_off = n1; n1 += b.kv; }
+                if (d.gated) { b.g_off = n1; n1 += d.heads * d.vdim; }
+                b.a_off = ko; ko += d.heads * d.vdim;
+                if (d.rot_dims > 0) {
+                    // frequencies in double, rounded once: base^(-2k/dims); long wavelengths slowed down by rot_factor, a linear blend between
+                    b.inv_freq.resize(d.rot_dims / 2);
+                    for (int k = 0; k < d.rot_dims / 2; k++) {
+                        double f = pow((double)d.rot_base, -2.0 * k / d.rot_dims);
+                        if (d.rot_factor > 0.0f) {
+                            const double wl = 2.0 * M_PI / f, orig = d.rot_original, lo = d.rot_low, hi = d.rot_high, fac = d.rot_factor;
+                            if (wl > orig / lo) f = f / fac;
+                            else if (!(wl < orig / hi)) { const double sm = (orig / wl - lo) / (hi - lo); f = (1.0 - sm) * f / fac + sm * f; }
+                        }
+                        b.inv_freq[k] = (float)f;
+                    }
+                    TRY(dalloc_t(m, &b.d_inv_freq, b.inv_freq.size()));
+                    GTB_CUDA(cudaMemcpyAsync(b.d_inv_freq, b.inv_freq.data(), b.inv_freq.size() * sizeof(float), cudaMemcpyHostToDevice, ctx().stream));
+                }
+                continue;
+            }
             b.q_off = n1; b.k_off = n1 + b.kq; b.v_off = b.k_off + b.kk; n1 = b.v_off + b.kv;
             if (d.kind == GTB_MIX_RETENTION && d.gated) { b.g_off = n1; n1 += d.heads * d.vdim; }
             b.a_off = ko; ko += d.heads * d.vdim;
@@ -449,46 +626,106 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 }
             }
         }
-        GTB_CUDA(cudaStreamSynchronize(ctx().stream));       // the decay vectors above are read from temporaries of this loop
+        GTB_CUDA(cudaStreamSynchronize(ctx().stream));       // the vectors above are read from members that may move; wait for the copies
         l.n1 = n1;
-        l.kout = ko + l.ff;
+        l.kout = post ? ko : ko + l.ff;
         l.kout_p = pad64(l.kout);
         TRY(dalloc_t(m, &l.w_mix, (size_t)n1 * wp));
         TRY(dalloc_t(m, &l.w_out, (size_t)W * l.kout_p));
         for (int bi = 0; bi < l.d.n_branches; bi++) {
             BranchW& b = l.br[bi];
-            const std::string bp = lp + "mix." + (b.d.name[0] ? std::string(b.d.name) + "." : std::string());
+            const gtb_seq_branch& d = b.d;
+            const std::string bp = lp + "mix." + (d.name[0] ? std::string(d.name) + "." : std::string());
+            if (d.kind == GTB_MIX_MINGRU) {
+                TRY(dalloc_t(m, &l.d_bias, n1));
+                want_matrix(m, bp + "z", l.w_mix + (size_t)b.q_off * wp, d.dim, W, wp);
+                want_matrix(m, bp + "x", l.w_mix + (size_t)b.k_off * wp, d.dim, W, wp);
+                want_matrix(m, bp + "g", l.w_mix + (size_t)b.g_off * wp, d.dim, W, wp);
+                want_vector(m, bp + "z.b", l.d_bias + b.q_off, d.dim, 0);
+                want_vector(m, bp + "x.b", l.d_bias + b.k_off, d.dim, 0);
+                want_matrix(m, bp + "o", l.w_out + b.a_off, W, d.dim, l.kout_p);
+                continue;
+            }
             want_matrix(m, bp + "q", l.w_mix + (size_t)b.q_off * wp, b.kq, W, wp);
-            want_matrix(m, bp + "k", l.w_mix + (size_t)b.k_off * wp, b.kk, W, wp);
-            want_matrix(m, bp + "v", l.w_mix + (size_t)b.v_off * wp, b.kv, W, wp);
-            if (b.d.kind == GTB_MIX_RETENTION && b.d.gated) want_matrix(m, bp + "g", l.w_mix + (size_t)b.g_off * wp, b.d.heads * b.d.vdim, W, wp);
-            want_matrix(m, bp + "o", l.w_out + b.a_off, W, b.d.heads * b.d.vdim, l.kout_p);
-            if (b.d.kind == GTB_MIX_SIGMOID_ATTN) {
-                TRY(dalloc_t(m, &b.d_pb, b.d.heads));
-                want_vector(m, bp + "pb", b.d_pb, b.d.heads, 0);
+            const bool own_kv = !(d.kind == GTB_MIX_SOFTMAX_ATTN && d.kv_from >= 0);
+            if (own_kv) {
+                want_matrix(m, bp + "k", l.w_mix + (size_t)b.k_off * wp, b.kk, W, wp);
+                want_matrix(m, bp + "v", l.w_mix + (size_t)b.v_off * wp, b.kv, W, wp);
+            }
+            if ((d.kind == GTB_MIX_RETENTION || d.kind == GTB_MIX_SOFTMAX_ATTN) && d.gated) want_matrix(m, bp + "g", l.w_mix + (size_t)b.g_off * wp, d.heads * d.vdim, W, wp);
+            want_matrix(m, bp + "o", l.w_out + b.a_off, W, d.heads * d.vdim, l.kout_p);
+            if (d.kind == GTB_MIX_SIGMOID_ATTN) {
+                TRY(dalloc_t(m, &b.d_pb, d.heads));
+                want_vector(m, bp + "pb", b.d_pb, d.heads, 0);
+            }
+            if (d.kind == GTB_MIX_SOFTMAX_ATTN) {
+                if (d.qk_norm == 2) {
+                    TRY(dalloc_t(m, &b.d_qnorm, d.dim));
+                    want_vector(m, bp + "q.norm", b.d_qnorm, d.dim, 0);
+                    if (own_kv) { TRY(dalloc_t(m, &b.d_knorm, d.dim)); want_vector(m, bp + "k.norm", b.d_knorm, d.dim, 0); }
+                }
+                if (d.sink) { TRY(dalloc_t(m, &b.d_sink, d.heads)); want_vector(m, bp + "sink", b.d_sink, d.heads, 0); }
             }
         }
-        if (l.ff > 0) {
-            TRY(dalloc_t(m, &l.w_gu, (size_t)2 * l.ff * wp));
-            l.gu_inter = l.ff % 32 == 0;
-            want_matrix(m, lp + "mlp.gate", l.w_gu, l.ff, W, wp);
-            want_matrix(m, lp + "mlp.up", l.w_gu + (size_t)(l.gu_inter ? 32 : l.ff) * wp, l.ff, W, wp);
-            if (l.gu_inter)
-                for (const char* nm : {"mlp.gate", "mlp.up"}) { TensorDest& d = m->tensors[lp + nm]; d.group = 32; d.group_stride = 64; }
-            want_matrix(m, lp + "mlp.down", l.w_out + ko, W, l.ff, l.kout_p);
-        }
-        TRY(dalloc_t(m, &l.d_gain, 1));
-        want_vector(m, lp + "norm1", l.d_gain, 0, 0, true);
-        if (c.taps > 0) {
-            TRY(dalloc_t(m, &l.canon_a, (size_t)W * c.taps));
-            want_matrix(m, lp + "canon1", l.canon_a, W, c.taps, c.taps);
+        if (post) {
+            TRY(dalloc_t(m, &l.norm1, W));
+            want_vector(m, lp + "norm1", l.norm1, W, 0);
             if (l.ff > 0) {
-                TRY(dalloc_t(m, &l.canon_b, (size_t)W * c.taps));
-                want_matrix(m, lp + "canon2", l.canon_b, W, c.taps, c.taps);
+                TRY(dalloc_t(m, &l.norm2, W));
+                want_vector(m, lp + "norm2", l.norm2, W, 0);
+                l.kfp = pad64(l.ff);
+                m->kfp_max = std::max(m->kfp_max, l.kfp);
+                if (l.d.ff_kind == GTB_FF_POLYNORM) {
+                    TRY(dalloc_t(m, &l.w_up, (size_t)l.ff * wp));
+                    TRY(dalloc_t(m, &l.w_down, (size_t)W * l.kfp));
+                    TRY(dalloc_t(m, &l.d_act, 4));
+                    want_matrix(m, lp + "mlp.up", l.w_up, l.ff, W, wp);
+                    want_matrix(m, lp + "mlp.down", l.w_down, W, l.ff, l.kfp);
+                    want_vector(m, lp + "mlp.act", l.d_act, 4, 0);
+                    m->g_cols = std::max(m->g_cols, l.ff);
+                    m->kout_p_max = std::max(m->kout_p_max, l.kfp);
+                } else {
+                    const int E = l.d.experts, I = l.d.identity;
+                    REQ(E >= 0 && I >= 0 && E + I > 0 && E + I <= 4096 && l.d.top > 0 && l.d.top <= E + I && l.d.top <= 64);
+                    l.n_out = E + I;
+                    TRY(dalloc_t(m, &l.w_router, (size_t)l.n_out * wp));
+                    TRY(dalloc_t(m, &l.d_corr, l.n_out));
+                    want_matrix(m, lp + "mlp.router", l.w_router, l.n_out, W, wp);
+                    want_vector(m, lp + "mlp.correction", l.d_corr, l.n_out, 0);
+                    TRY(dalloc_t(m, &l.w_up, (size_t)std::max(E, 1) * l.ff * wp));
+                    TRY(dalloc_t(m, &l.w_down, (size_t)std::max(E, 1) * W * l.kfp));
+                    for (int e = 0; e < E; e++) {
+                        const std::string ep = lp + "mlp.e" + std::to_string(e) + ".";
+                        want_matrix(m, ep + "up", l.w_up + (size_t)e * l.ff * wp, l.ff, W, wp);
+                        want_matrix(m, ep + "down", l.w_down + (size_t)e * W * l.kfp, W, l.ff, l.kfp);
+                    }
+                    m->n_out_max = std::max(m->n_out_max, l.n_out);
+                    m->top_max = std::max(m->top_max, l.d.top);
+                }
+            }
+        } else {
+            if (l.ff > 0) {
+                TRY(dalloc_t(m, &l.w_gu, (size_t)2 * l.ff * wp));
+                l.gu_inter = l.ff % 32 == 0;
+                want_matrix(m, lp + "mlp.gate", l.w_gu, l.ff, W, wp);
+                want_matrix(m, lp + "mlp.up", l.w_gu + (size_t)(l.gu_inter ? 32 : l.ff) * wp, l.ff, W, wp);
+                if (l.gu_inter)
+                    for (const char* nm : {"mlp.gate", "mlp.up"}) { TensorDest& d = m->tensors[lp + nm]; d.group = 32; d.group_stride = 64; }
+                want_matrix(m, lp + "mlp.down", l.w_out + ko, W, l.ff, l.kout_p);
+                m->ff_max = std::max(m->ff_max, l.ff);
+            }
+            TRY(dalloc_t(m, &l.d_gain, 1));
+            want_vector(m, lp + "norm1", l.d_gain, 0, 0, true);
+            if (c.taps > 0) {
+                TRY(dalloc_t(m, &l.canon_a, (size_t)W * c.taps));
+                want_matrix(m, lp + "canon1", l.canon_a, W, c.taps, c.taps);
+                if (l.ff > 0) {
+                    TRY(dalloc_t(m, &l.canon_b, (size_t)W * c.taps));
+                    want_matrix(m, lp + "canon2", l.canon_b, W, c.taps, c.taps);
+                }
             }
         }
         m->n1_max = std::max(m->n1_max, n1);
-        m->ff_max = std::max(m->ff_max, l.ff);
         m->kout_p_max = std::max(m->kout_p_max, l.kout_p);
         for (int bi = 0; bi < l.d.n_branches; bi++)
             if (l.br[bi].d.kind == GTB_MIX_RETENTION) m->ro_max = std::max(m->ro_max, l.br[bi].d.heads * l.br[bi].d.vdim);
@@ -510,13 +747,26 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
         size_t per_slot = 0;
         for (int bi = 0; bi < l.d.n_branches; bi++) {
             const gtb_seq_branch& d = l.br[bi].d;
-            if (d.kind == GTB_MIX_SIGMOID_ATTN) {
-                const size_t kb = (size_t)c.max_ctx * d.kv_heads * d.dim * es, vb = (size_t)c.max_ctx * d.kv_heads * d.vdim * es;
-                TRY(dalloc(m, &r.kc[bi], kb * c.n_slots));
-                TRY(dalloc(m, &r.vc[bi], vb * c.n_slots));
-                per_slot += kb + vb;
+            if (d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_SOFTMAX_ATTN) {
+                if (d.kind == GTB_MIX_SOFTMAX_ATTN && d.kv_from >= 0) {
+                    // no loop (checked above), so run j is layer j: the source layer's cache, appended to earlier in the same pass
+                    r.kc[bi] = m->runs[d.kv_from].kc[0];
+                    r.vc[bi] = m->runs[d.kv_from].vc[0];
+                } else {
+                    const size_t kb = (size_t)c.max_ctx * d.kv_heads * d.dim * es, vb = (size_t)c.max_ctx * d.kv_heads * d.vdim * es;
+                    TRY(dalloc(m, &r.kc[bi], kb * c.n_slots));
+                    TRY(dalloc(m, &r.vc[bi], vb * c.n_slots));
+                    per_slot += kb + vb;
+                }
+                if (d.kind == GTB_MIX_SOFTMAX_ATTN && d.window > 0 && d.pool > 0) {      // pooled blocks follow this layer's own block size
+                    r.max_blocks = c.max_ctx / d.pool + 1;
+                    const size_t kb = (size_t)r.max_blocks * d.kv_heads * d.dim * sizeof(float), vb = (size_t)r.max_blocks * d.kv_heads * d.vdim * sizeof(float);
+                    TRY(dalloc(m, (void**)&r.pk, kb * c.n_slots));
+                    TRY(dalloc(m, (void**)&r.pv, vb * c.n_slots));
+                    per_slot += kb + vb;
+                }
             } else {
-                const size_t sb = (size_t)d.heads * d.dim * d.vdim * sizeof(float);
+                const size_t sb = state_floats(d) * sizeof(float);
                 TRY(dalloc(m, (void**)&r.state[bi], sb * c.n_slots));
                 per_slot += sb;
             }
@@ -534,7 +784,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     TRY(dalloc_t(m, &m->h, R * W));
     TRY(dalloc_t(m, &m->Y, R * W));
     TRY(dalloc_t(m, &m->P, R * m->n1_max));
-    TRY(dalloc_t(m, &m->G, R * 2 * std::max(m->ff_max, 1)));
+    TRY(dalloc_t(m, &m->G, R * std::max(std::max(2 * m->ff_max, m->g_cols), 1)));
     TRY(dalloc_t(m, &m->O, R * std::max(m->ro_max, 1)));
     for (const LayerW& l : m->L)
         for (int bi = 0; bi < l.d.n_branches; bi++)
@@ -544,6 +794,15 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 m->retU_floats = std::max(m->retU_floats, chunks * d.heads * d.dim * d.vdim);
             }
     if (m->retU_floats) TRY(dalloc_t(m, &m->retU, m->retU_floats));
+    for (const LayerW& l : m->L)
+        if (l.br[0].d.kind == GTB_MIX_MINGRU) m->gruAB_floats = std::max(m->gruAB_floats, (R / GRU_CHUNK + c.n_slots + 1) * 2 * (size_t)l.br[0].d.dim);
+    if (m->gruAB_floats) TRY(dalloc_t(m, &m->gruAB, m->gruAB_floats));
+    if (m->n_out_max > 0) {
+        TRY(dalloc_t(m, &m->rl, R * m->n_out_max));
+        TRY(dalloc_t(m, &m->sel_idx, R * m->top_max));
+        TRY(dalloc_t(m, &m->sel_w, R * m->top_max));
+        TRY(dalloc(m, &m->act, R * m->top_max * m->kfp_max * es));
+    }
     {   // key splits of decode-time attention: one CTA per 128 keys of a full slot, at most 32
         int hv = 0;
         for (const LayerW& l : m->L)
@@ -638,7 +897,7 @@ int gtb_seq_slot_reset(gtb_seq_t m, int slot) {
         const LayerW& l = m->L[r.layer];
         for (int bi = 0; bi < l.d.n_branches; bi++)
             if (r.state[bi]) {
-                const size_t sb = (size_t)l.br[bi].d.heads * l.br[bi].d.dim * l.br[bi].d.vdim * sizeof(float);
+                const size_t sb = state_floats(l.br[bi].d) * sizeof(float);
                 GTB_CUDA(cudaMemsetAsync((char*)r.state[bi] + sb * slot, 0, sb, st));
             }
         if (r.tail) {
@@ -882,6 +1141,7 @@ int gtb_seq_set_option(gtb_seq_t m, const char* name, int value) {
     else if (n == "graph") m->use_graph = value != 0;
     else if (n == "fused_attn") m->fused_attn = value != 0;
     else if (n == "fused_norm") m->fused_norm = value != 0;
+    else if (n == "grouped_experts") m->grouped_experts = value != 0;
     else return gtb::fail(GTB_ERR_ARG, "unknown option '%s'", name);
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     return GTB_OK;

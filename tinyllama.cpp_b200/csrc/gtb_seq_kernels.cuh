@@ -124,15 +124,15 @@ __global__ void k_commit(PassTables t, int S) {
 }
 
 // ------------------------------------------------------------------------------------------------ embedding
-// x = embed[tok] (+ bigram[(prev * mul_prev + tok * mul_cur) mod buckets], row `buckets` for a sequence's first token); x0 = x
+// x = scale * embed[tok] (+ bigram[(prev * mul_prev + tok * mul_cur) mod buckets], row `buckets` for a sequence's first token); x0 = x
 __global__ void k_embed(PassTables t, const bf16* __restrict__ embed, const bf16* __restrict__ bigram, int buckets, int mul_prev,
-                        int mul_cur, int width, float* __restrict__ x, float* __restrict__ x0) {
+                        int mul_cur, int width, float scale, float* __restrict__ x, float* __restrict__ x0) {
     const int r = blockIdx.x;
     const int tok = t.tok[r], prev = t.row_prev[r];
     long long row = buckets;
     if (prev >= 0) row = ((long long)prev * mul_prev + (long long)tok * mul_cur) % buckets;
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float v = __bfloat162float(embed[(size_t)tok * width + c]);
+        float v = __bfloat162float(embed[(size_t)tok * width + c]) * scale;
         if (buckets > 0) v += __bfloat162float(bigram[(size_t)row * width + c]);
         x[(size_t)r * width + c] = v;
         if (x0) x0[(size_t)r * width + c] = v;

@@ -8,11 +8,12 @@ import json
 from pathlib import Path
 
 
-def _open_reninex(path: Path, dtype: str, n_slots: int, max_ctx: int, max_rows: int = 0, device: int = 0):
-    from . import reninex, seq
+def _open_described(family, path: Path, dtype: str, n_slots: int, max_ctx: int, max_rows: int = 0, device: int = 0):
+    """A family of the layer-list library: `family` is its module (read_checkpoint, tensor_shapes)."""
+    from . import seq
     seq.init(device)
-    desc, tensors = reninex.read_checkpoint(path)
-    known = reninex.tensor_shapes(desc)
+    desc, tensors = family.read_checkpoint(path)
+    known = family.tensor_shapes(desc)
     extra = sorted(set(tensors) - set(known))
     if extra:                                   # e.g. a filter of a feed-forward that the layer does not have
         import sys
@@ -34,7 +35,18 @@ def _open_tinyllama(path: Path, dtype: str, n_slots: int, max_ctx: int, max_rows
     return e
 
 
-FAMILIES = {"Reninex": _open_reninex, "TinyLlama": _open_tinyllama}
+def _open_reninex(path: Path, dtype: str, n_slots: int, max_ctx: int, **kw):
+    from . import reninex
+    return _open_described(reninex, path, dtype, n_slots, max_ctx, **kw)
+
+
+def _open_robopel(path: Path, dtype: str, n_slots: int, max_ctx: int, **kw):
+    from . import robopel
+    return _open_described(robopel, path, dtype, n_slots, max_ctx, **kw)
+
+
+FAMILIES = {"Reninex": _open_reninex, "Robopel": _open_robopel, "TinyLlama": _open_tinyllama}
+STEPWISE = {"Reninex", "Robopel"}          # families of the layer-list library: slots, portion-wise step function, scheduler
 
 
 def family_of(path) -> str:

@@ -117,16 +117,7 @@ def read_checkpoint(model_dir) -> tuple[dict, dict]:
     """(description, name -> bfloat16 bit patterns) of a folder with config.json and model.safetensors."""
     model_dir = Path(model_dir)
     desc = describe(json.loads((model_dir / "config.json").read_text()))
-    tensors, known = {}, tensor_shapes(desc)
-    for name, (dt, arr) in st.read(model_dir / "model.safetensors").items():
-        if dt == "BF16":
-            tensors[name] = arr
-        elif dt in ("F32", "F16"):
-            tensors[name] = st.f32_to_bf16_bits(arr.astype(np.float32))
-        elif name in known:
-            raise ValueError(f"tensor {name}: dtype {dt} where a {ARCHITECTURE} checkpoint holds bfloat16")
-        # tensors of other types that the description does not use are left out (the opener reports unused names)
-    return desc, tensors
+    return desc, st.read_as_bf16(model_dir / "model.safetensors", tensor_shapes(desc), ARCHITECTURE)
 
 
 def write_checkpoint(model_dir, cfg: dict, tensors: dict) -> None:

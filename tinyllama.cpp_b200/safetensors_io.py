@@ -53,3 +53,17 @@ def write(path, tensors: dict) -> None:
         f.write(h)
         for b in blobs:
             f.write(b)
+
+
+def read_as_bf16(path, known: dict, family: str) -> dict:
+    """name -> bfloat16 bit patterns of a checkpoint whose family stores bfloat16: float16 / float32 tensors are converted, tensors of
+    other types are left out unless the description (known: name -> shape) needs them, which is an error."""
+    out = {}
+    for name, (dt, arr) in read(path).items():
+        if dt == "BF16":
+            out[name] = arr
+        elif dt in ("F32", "F16"):
+            out[name] = f32_to_bf16_bits(arr.astype(np.float32))
+        elif name in known:
+            raise ValueError(f"tensor {name}: dtype {dt} where a {family} checkpoint holds bfloat16")
+    return out
