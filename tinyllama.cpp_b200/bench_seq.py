@@ -1,5 +1,6 @@
 """`bench.py --workload reninex`: prefill and decode throughput of the Reninex family at layer sizes that resemble a real model
-(random weights), beside TinyLlama at the same layer shape and layer count.  Timed with CUDA events on each library's own stream,
+(random weights), beside TinyLlama at the same layer shape and layer count.  `bench.py --workload robopel`: the same for the Robopel
+family, beside Reninex (the closest existing model: same library, same width and layer count).  Timed with CUDA events on each library's own stream,
 after warm-up; the weights of one pass (hundreds of MB) are larger than L2, so every pass streams them from HBM."""
 from __future__ import annotations
 
@@ -129,6 +130,110 @@ def reninex_section(torch, name, layers, T, iters, warmup, peaks):
     return out
 
 
+ROBOPEL_SIZES = {
+    # width, dense ff, minGRU width, attention (heads, kv, dim), window, pool, experts x ff (top of experts + identity)
+    "w2048": dict(width=2048, ff=5632, gru=2048, heads=32, kv=4, dim=64, window=1024, pool=16, experts=16, identity=2, top=2, eff=1408),
+    "w1024": dict(width=1024, ff=2816, gru=1024, heads=16, kv=4, dim=64, window=512, pool=8, experts=16, identity=2, top=2, eff=704),
+}
+
+
+def robopel_config(name, vocab=32000):
+    """Four layers in the family's usual order: minGRU + dense, attention + experts, minGRU + experts, attention on layer 1's cache + dense."""
+    from . import robopel as RP
+    z = ROBOPEL_SIZES[name]
+    att = dict(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["dim"], window=z["window"], pool=z["pool"], rot_dims=z["dim"], rot_base=500000.0,
+               scaling=(8.0, 1.0, 4.0, 8192), softcap=30.0)
+    moe = lambda: RP.moe_mlp(experts=z["experts"], identity=z["identity"], top=z["top"], ff=z["eff"])
+    layers = [RP.mingru_layer(z["gru"], mlp=RP.dense_mlp(z["ff"])), RP.attention_layer(mlp=moe(), **att), RP.mingru_layer(z["gru"], mlp=moe()),
+              RP.attention_layer(kv_from=1, mlp=RP.dense_mlp(z["ff"]), **att)]
+    return RP.make_config(vocab=vocab, width=z["width"], layers=layers, embed_scale=float(z["width"]) ** 0.5, eps=1e-6)
+
+
+def robopel_counts(desc, T):
+    """(weights every token multiplies, FLOPs of the mixers' own arithmetic for a T-token prompt, bytes of weights a decode step of one
+    sequence reads) -- routed experts count `top` experts per token."""
+    from .seq import FF_EXPERTS, MIX_MINGRU
+    W, params, mix, dec = desc["width"], 0, 0.0, 0
+    for l in desc["layers"]:
+        b = l["branches"][0]
+        if b["kind"] == MIX_MINGRU:
+            per = 4 * W * b["dim"]
+            mix += 10.0 * b["dim"] * T
+        else:
+            hv = b["heads"] * b["vdim"]
+            per = W * (b["heads"] * b["dim"] + 2 * hv) + (W * b["kv_heads"] * (b["dim"] + b["vdim"]) if b["kv_from"] < 0 else 0)
+            win, pool = b.get("window", 0), b.get("pool", 0)
+            keys = sum(min(i + 1, win) + ((i - win + 1) // pool if pool and i - win + 1 >= pool else 0) for i in range(T)) if win else T * (T + 1) / 2
+            mix += 2.0 * b["heads"] * (b["dim"] + b["vdim"]) * keys
+        if l["ff"]:
+            per += (W * (l["experts"] + l["identity"]) + l["top"] * 2 * W * l["ff"]) if l.get("ff_kind") == FF_EXPERTS else 2 * W * l["ff"]
+        params += per
+    return params + desc["vocab"] * W, mix, 2 * (params + desc["vocab"] * W)
+
+
+def robopel_section(torch, name, T, iters, warmup, peaks):
+    from . import robopel as RP, seq
+    cfg = robopel_config(name)
+    desc = RP.describe(cfg)
+    t0 = time.time()
+    rng = np.random.default_rng(0)
+    tensors = {}
+    for k, shape in RP.tensor_shapes(desc).items():              # cheap random bf16 patterns of the right scale
+        n = int(np.prod(shape))
+        leaf = k.split(".")[-1]
+        if leaf in ("norm1", "norm2") or k == "final.norm" or leaf in ("correction", "b"):
+            a = np.zeros(n, np.uint16)
+        elif k.endswith("q.norm") or k.endswith("k.norm"):
+            a = np.full(n, 0x3F80, np.uint16)
+        elif leaf == "act":
+            a = RP.st.f32_to_bf16_bits(np.array([0.6, 0.3, 0.2, 0.05], np.float32))
+        else:
+            std = 1.0 / desc["embed_scale"] if k == "embed" else (1.0 if leaf == "sink" else 1.0 / np.sqrt(shape[-1]))
+            a = RP.st.f32_to_bf16_bits(rng.standard_normal(n, np.float32) * np.float32(std))
+        tensors[k] = a.reshape(shape)
+    n_slots = 8
+    m = seq.SeqModel(desc, seq.BF16, n_slots, T + 64, max_rows=T).load(tensors)
+    stream = torch.cuda.ExternalStream(seq.stream_handle(), device=torch.device("cuda", 0))
+    prompt = rng.integers(0, desc["vocab"], T).astype(np.int32)
+    params, mix, dec_bytes = robopel_counts(desc, T)
+    out = {"size": name, "layers": len(desc["layers"]), "params_matmul_per_token": params, "weight_bytes": m.weight_bytes(), "setup_s": round(time.time() - t0, 1)}
+
+    def prefill():
+        m.reset(0)
+        m.step([(0, prompt)], [T - 1])
+    l0 = seq.launch_count()
+    prefill()
+    out["prefill_launches"] = seq.launch_count() - l0
+    ms = _events(torch, stream, prefill, iters, warmup)
+    flops = 2.0 * T * params - 2.0 * (T - 1) * desc["vocab"] * desc["width"] + mix
+    out["prefill"] = {"T": T, "ms": ms, "tokens_per_s": T / ms * 1e3, "tflops": flops / ms * 1e-9, "frac_of_bf16_peak": flops / ms * 1e-9 / peaks["tflops"],
+                      "note": "includes the host->device copy of the prompt and the device->host copy of the last row's logits; experts count top per token"}
+    for s in range(n_slots):
+        m.reset(s)
+        m.step_greedy([(s, prompt[: T - 40])])
+    state_bytes = m.state_bytes_per_slot() * (T - 40) / (T + 64)
+    for nseq in (1, 8):
+        slots, steps = list(range(nseq)), 8
+        m.decode(slots, 2)
+        t_ms = []
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                m.decode(slots, steps)
+                b.record(stream)
+                torch.cuda.synchronize()
+                t_ms.append(a.elapsed_time(b) / steps)
+        ms = float(np.median(t_ms))
+        by = dec_bytes - 2 * desc["vocab"] * desc["width"]        # the embedding table is read one row per sequence
+        out[f"decode_{nseq}"] = {"ms_per_step": ms, "tokens_per_s": nseq / ms * 1e3, "bytes_per_step_one_sequence": by, "gbs": by / ms * 1e-6,
+                                 "frac_of_hbm_peak": by / ms * 1e-6 / peaks["hbm_gbs"],
+                                 "note": "bytes: weights one sequence's step reads (top experts per routed layer); further sequences add their experts and state"}
+    out["state_bytes_per_slot_at_T"] = state_bytes
+    m.close()
+    return out
+
+
 def tinyllama_section(torch, layers, T, iters, warmup, peaks):
     """The closest existing model at the same layer shape (width 2048, ff 5632) and layer count: FP16 weights."""
     from . import capi, weights as W
@@ -176,6 +281,37 @@ def tinyllama_section(torch, layers, T, iters, warmup, peaks):
             out["decode_q8_order_free"] = {"ms_per_step": ms, "tokens_per_s": 1e3 / ms, "gbs": by / ms * 1e-6, "frac_of_hbm_peak": by / ms * 1e-6 / peaks["hbm_gbs"]}
         eng.close()
     return out
+
+
+def run_robopel(args, root, clock_sampler) -> None:
+    """`--workload robopel`: Robopel at two sizes, Reninex at the same widths and layer count in the same call."""
+    import torch
+    from . import build, seq
+    build.build(target="seq")
+    torch.cuda.set_device(0)
+    p = root / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        peaks = {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d.get("bf16_tflops", 1590.0)), "source": "measured (MEASURED_PEAKS.json)"}
+    else:
+        peaks = {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
+    seq.init(0)
+    T = 2048
+    iters = max(3, min(args.steps if args.steps != 512 else 5, 20))
+    warm = max(args.warmup if args.warmup != 16 else 3, 3)
+    res = {"robopel": [], "reninex_same_width": [], "peaks": peaks}
+    with clock_sampler(0) as clk:
+        for name in ROBOPEL_SIZES:
+            res["robopel"].append(robopel_section(torch, name, T, iters, warm, peaks))
+        for name in SIZES:
+            res["reninex_same_width"].append(reninex_section(torch, name, 4, T, iters, warm, peaks))
+    head = res["robopel"][0]
+    print(json.dumps({"metric": "robopel_prefill_tokens_per_s", "value": head["prefill"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "steps": iters, "warmup": warm, "ms_per_step": head["prefill"]["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16 operands, fp32 accumulation; fp32 stream, scores, state", "data": "synthetic",
+                      "config": {"workload": f"Robopel {head['size']} x {head['layers']} layers, random weights: prefill of {T} tokens; decode at that context",
+                                 "l2": "weights of a pass exceed L2"},
+                      "detail": res, "gpu_launches": head["prefill_launches"], "clocks": clk.summary()}), flush=True)
 
 
 def run(args, root, clock_sampler) -> None:

@@ -24,6 +24,7 @@
 #include "gtb_seq_gemm.h"
 #include "gtb_seq_kernels.cuh"
 #include "gtb_seq_mixers.cuh"
+#include "gtb_seq_mixers_tiled.cuh"
 
 using namespace gtb;
 using namespace gtb::seq;
@@ -110,6 +111,11 @@ struct gtb_seq_model {
     int* sel_idx = nullptr;                      // chosen router outputs [max_rows][top_max]
     float* sel_w = nullptr;
     void* act = nullptr;                         // expert activations [max_rows * top_max][kfp_max]
+    // grouped experts (bf16 mode): rows sorted by expert, groups aligned to 128 rows
+    int mpad_max = 0, e_max = 0;
+    bf16 *Xg = nullptr, *actg = nullptr;         // [mpad_max][wp], [mpad_max][kfp_max]
+    float *Yg = nullptr, *rw = nullptr;          // [mpad_max][width], [mpad_max]
+    int *pair_dst = nullptr, *tile_e = nullptr;  // [max_rows * top_max], [mpad_max / 128]
     int n_out_max = 0, top_max = 0, kfp_max = 0, g_cols = 0;
     bool grouped_experts = true;
     float* cap = nullptr;                        // [runs][max_rows][width]
@@ -253,6 +259,25 @@ RetLaunch ret_launch(const gtb_seq_branch& d) {
     return r;
 }
 
+template <int DP, int VP>
+int launch_sattn_mma(const PassTables& t, const SoftAttn& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, const float* pk, const float* pv,
+                     bf16* out, int ld_out) {
+    const size_t smem = (3 * 64 * (size_t)(DP + 8) + 2 * 64 * (size_t)(VP + 8)) * 2;      // queries + two stages of keys and values
+    static bool attr = false;
+    if (!attr) { GTB_CUDA(cudaFuncSetAttribute(k_sattn_mma<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
+    k_sattn_mma<DP, VP><<<dim3(n_tiles, a.heads), 128, smem, ctx().stream>>>(t, a, S, P, ldp, kc, vc, pk, pv, out, ld_out);
+    GTB_LAUNCHED();
+    return GTB_OK;
+}
+int sattn_mma(const PassTables& t, const SoftAttn& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, const float* pk, const float* pv,
+              bf16* out, int ld_out) {
+    const int dp = a.dim <= 32 ? 32 : a.dim <= 64 ? 64 : 128, vp = a.vdim <= 32 ? 32 : a.vdim <= 64 ? 64 : 128;
+#define SA_CASE(D, V) if (dp == D && vp == V) return launch_sattn_mma<D, V>(t, a, S, n_tiles, P, ldp, kc, vc, pk, pv, out, ld_out)
+    SA_CASE(32, 32); SA_CASE(32, 64); SA_CASE(32, 128); SA_CASE(64, 32); SA_CASE(64, 64); SA_CASE(64, 128); SA_CASE(128, 32); SA_CASE(128, 64); SA_CASE(128, 128);
+#undef SA_CASE
+    return -1;
+}
+
 GruBranch gru_args(const BranchW& b) {
     GruBranch a{};
     a.width = b.d.dim; a.z_off = b.q_off; a.x_off = b.k_off; a.g_off = b.g_off; a.a_off = b.a_off;
@@ -273,7 +298,7 @@ SoftAttn soft_args(const gtb_seq_model* m, const BranchW& b, const Run& run) {
 // One layer of the post-norm style on R rows: x += norm1(mixer(x)); x += norm2(ff(x)).  opA holds the stream as a product operand
 // when x_in_opA (the residual update of the previous sublayer wrote it) and always does on return.
 template <typename OT>
-int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, const LayerW& l, bool portions, const int* seg_lens, bool x_in_opA) {
+int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, const LayerW& l, bool portions, const int* seg_lens, int n_qtiles, bool x_in_opA) {
     cudaStream_t st = ctx().stream;
     const gtb_seq_config& c = m->cfg;
     const int W = c.width, wp = m->wp;
@@ -310,12 +335,18 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
             k_pool_update<OT><<<R, 128, 0, st>>>(t, a, (const OT*)run.kc[0], (const OT*)run.vc[0], run.pk, run.pv);
             GTB_LAUNCHED();
         }
-        k_sattn<OT><<<dim3(R, a.heads), 128, (a.dim + 128 + 33) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[0], (const OT*)run.vc[0], run.pk, run.pv, opC, l.kout_p);
-        GTB_LAUNCHED();
+        int done = -1;
+        if (portions && sizeof(OT) == 2 && a.dim <= 128 && a.vdim <= 128)
+            done = sattn_mma(t, a, S, n_qtiles, m->P, l.n1, (const bf16*)run.kc[0], (const bf16*)run.vc[0], run.pk, run.pv, (bf16*)opC, l.kout_p);
+        if (done > 0) return done;
+        if (done < 0) {
+            k_sattn<OT><<<dim3(R, a.heads), 128, (a.dim + 128 + 33) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[0], (const OT*)run.vc[0], run.pk, run.pv, opC, l.kout_p);
+            GTB_LAUNCHED();
+        }
     }
     rc = product<OT>(m, opC, l.kout_p, l.w_out, l.kout_p, m->Y, W, R, W, l.kout_p, nullptr, 0);
     if (rc) return rc;
-    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm1, nullptr, nullptr, 0, 0, m->x, opA, wp);
+    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm1, nullptr, nullptr, 0, 0, nullptr, nullptr, m->x, opA, wp);
     GTB_LAUNCHED();
     if (l.ff == 0) return GTB_OK;
     if (l.d.ff_kind == GTB_FF_POLYNORM) {
@@ -325,7 +356,7 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         GTB_LAUNCHED();
         rc = product<OT>(m, opC, l.kfp, l.w_down, l.kfp, m->Y, W, R, W, l.kfp, nullptr, 0);
         if (rc) return rc;
-        k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, nullptr, nullptr, 0, 0, m->x, opA, wp);
+        k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, nullptr, nullptr, 0, 0, nullptr, nullptr, m->x, opA, wp);
         GTB_LAUNCHED();
         return GTB_OK;
     }
@@ -334,6 +365,23 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
     if (rc) return rc;
     k_moe_route<<<R, 32, 2 * l.n_out * sizeof(float), st>>>(m->rl, l.n_out, l.n_out, l.d_corr, top, m->sel_idx, m->sel_w);
     GTB_LAUNCHED();
+    const int n_pairs = R * top, mpad = (n_pairs + 127) / 128 * 128 + E * 128;
+    if (sizeof(OT) == 2 && E > 0 && m->grouped_experts && m->use_tensor && m->gp && m->Xg && R >= m->tensor_min_rows && mpad <= m->mpad_max) {
+        // rows sorted by expert, two grouped tensor-core products (up with the weighted relu^2 epilogue, down), the choices of a row summed
+        // in the residual update
+        k_moe_group<<<1, 1024, 2 * E * sizeof(int), st>>>(m->sel_idx, n_pairs, E, m->pair_dst, m->tile_e, mpad / 128);
+        GTB_LAUNCHED();
+        k_moe_gather<<<n_pairs, 128, 0, st>>>((const bf16*)opA, wp, top, m->pair_dst, m->sel_w, m->Xg, m->rw);
+        GTB_LAUNCHED();
+        rc = seq_gemm_bf16_grouped(m->gp, m->Xg, wp, l.w_up, wp, mpad, l.ff, wp, E, m->tile_e, nullptr, 0, m->actg, l.kfp, m->rw);
+        if (rc == 0) rc = seq_gemm_bf16_grouped(m->gp, m->actg, l.kfp, l.w_down, l.kfp, mpad, W, l.kfp, E, m->tile_e, m->Yg, W, nullptr, 0, nullptr);
+        if (rc > 0) return rc;
+        if (rc == 0) {
+            k_postnorm_add<OT><<<R, 256, 0, st>>>(nullptr, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, m->Yg, m->pair_dst, m->x, opA, wp);
+            GTB_LAUNCHED();
+            return GTB_OK;
+        }
+    }
     if (E > 0) {
         k_moe_up_rows<OT><<<dim3(R * top, std::max(1, std::min(8, (l.kfp + 7) / 8))), 256, 0, st>>>(opA, wp, wp, l.w_up, wp, l.ff, l.kfp, E, top, m->sel_idx, m->sel_w, (OT*)m->act);
         GTB_LAUNCHED();
@@ -342,7 +390,7 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
     } else {
         GTB_CUDA(cudaMemsetAsync(m->Y, 0, (size_t)R * W * sizeof(float), st));
     }
-    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, m->x, opA, wp);
+    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, nullptr, nullptr, m->x, opA, wp);
     GTB_LAUNCHED();
     return GTB_OK;
 }
@@ -369,7 +417,7 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
         const LayerW& l = m->L[run.layer];
         if (l.d.style == GTB_BLOCK_POSTNORM) {
             if (run.enters_pass) return gtb::fail(GTB_ERR_STATE, "a post-norm layer cannot open a loop pass");
-            int rc = run_postnorm_layer<OT>(m, t, R, S, run, l, portions, seg_lens, x_in_opA);
+            int rc = run_postnorm_layer<OT>(m, t, R, S, run, l, portions, seg_lens, n_qtiles, x_in_opA);
             if (rc) return rc;
             x_in_opA = true;
             if (m->capture) {
@@ -701,6 +749,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                     }
                     m->n_out_max = std::max(m->n_out_max, l.n_out);
                     m->top_max = std::max(m->top_max, l.d.top);
+                    m->e_max = std::max(m->e_max, E);
                 }
             }
         } else {
@@ -802,6 +851,15 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
         TRY(dalloc_t(m, &m->sel_idx, R * m->top_max));
         TRY(dalloc_t(m, &m->sel_w, R * m->top_max));
         TRY(dalloc(m, &m->act, R * m->top_max * m->kfp_max * es));
+        if (c.mode == GTB_SEQ_BF16 && m->e_max > 0) {
+            m->mpad_max = (int)((R * m->top_max + 127) / 128 * 128) + m->e_max * 128;
+            TRY(dalloc_t(m, &m->Xg, (size_t)m->mpad_max * wp));
+            TRY(dalloc_t(m, &m->actg, (size_t)m->mpad_max * m->kfp_max));
+            TRY(dalloc_t(m, &m->Yg, (size_t)m->mpad_max * W));
+            TRY(dalloc_t(m, &m->rw, m->mpad_max));
+            TRY(dalloc_t(m, &m->pair_dst, R * m->top_max));
+            TRY(dalloc_t(m, &m->tile_e, m->mpad_max / 128));
+        }
     }
     {   // key splits of decode-time attention: one CTA per 128 keys of a full slot, at most 32
         int hv = 0;

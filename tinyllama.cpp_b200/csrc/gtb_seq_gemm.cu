@@ -15,6 +15,10 @@
 //
 // The fused variant (EPI_GEGLU) takes W = gate rows and up rows interleaved in groups of 32 and writes gelu_tanh(gate) * up as a
 // bf16 operand block: the feed-forward activation never exists in fp32 in HBM.
+//
+// Grouped products (routed experts): the rows of A are sorted into groups that start on multiples of 128 rows, a device table gives
+// every M tile its group (or -1: nothing to do), and group g multiplies with rows [g N, (g + 1) N) of W.  EPI_RELU2 writes
+// row_w[row] * relu(acc)^2 as a bf16 operand block (the expert's activation, already weighted with the router's score).
 #include "gtb_seq_gemm.h"
 
 #include <cuda_bf16.h>
@@ -26,7 +30,7 @@ namespace gtb {
 namespace seq {
 
 constexpr int SQ_BM = 128, SQ_BK = 64, SQ_THREADS = 320, SQ_EPI_THREADS = 256;
-enum { SQ_EPI_F32 = 0, SQ_EPI_GEGLU = 1 };
+enum { SQ_EPI_F32 = 0, SQ_EPI_GEGLU = 1, SQ_EPI_RELU2 = 2 };
 
 template <int BN> struct SqCfg {
     static constexpr int STAGES = (BN == 256) ? 4 : 6;
@@ -47,6 +51,9 @@ struct SqEpi {
     __nv_bfloat16* act;      // EPI_GEGLU: output operand [M][ld_act], written at column act_off + (pair index)
     int ld_act, act_off;
     int* status;
+    const int* tile_group;   // grouped product: group of every M tile (-1: skip), or null
+    int group_rows;          // rows of W per group
+    const float* row_w;      // EPI_RELU2: weight of every row of A
 };
 
 // bounded wait: false when the barrier did not complete (or another role gave up)
@@ -107,12 +114,15 @@ k_seq_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
                 const int mt = tile % n_mt, nt = tile / n_mt;         // consecutive CTAs share one slice of W
+                const int grp = ep.tile_group ? ep.tile_group[mt] : 0;
+                if (grp < 0) continue;
+                const int wrow = grp * ep.group_rows + nt * BN;
                 for (int kb = 0; kb < nkb; kb++) {
                     if (!(ok = sq_wait(bar_empty(s), ph ^ 1, abort_flag))) break;
                     mbar_expect_tx(bar_full(s), Cfg::STAGE_BYTES);
                     const uint32_t sa = smem_base + s * Cfg::STAGE_BYTES;
                     tma_load_2d(sa, &tmA, bar_full(s), kb * SQ_BK, mt * SQ_BM);
-                    tma_load_2d(sa + Cfg::A_BYTES, &tmB, bar_full(s), kb * SQ_BK, nt * BN);
+                    tma_load_2d(sa + Cfg::A_BYTES, &tmB, bar_full(s), kb * SQ_BK, wrow);
                     if (++s == ST) { s = 0; ph ^= 1; }
                 }
             }
@@ -122,9 +132,10 @@ k_seq_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
             uint32_t s = 0, ph = 0;
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, it++) {
-                const int as = it & 1;
-                if (!(ok = sq_wait(bar_tempty(as), ((it >> 1) & 1) ^ 1, abort_flag))) break;
+            for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+                if (ep.tile_group && ep.tile_group[tile % n_mt] < 0) continue;      // skipped tiles take no accumulator stage
+                const int cur = it++, as = cur & 1;
+                if (!(ok = sq_wait(bar_tempty(as), ((cur >> 1) & 1) ^ 1, abort_flag))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(as * BN);
                 for (int kb = 0; kb < nkb; kb++) {
@@ -146,10 +157,11 @@ k_seq_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
         const int chalf = (warp - 2) >> 2;                          // which half of the tile's columns
         int it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, it++) {
+        for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
             const int mt = tile % n_mt, nt = tile / n_mt;
-            const int as = it & 1;
-            if (!(ok = sq_wait(bar_tfull(as), (it >> 1) & 1, abort_flag))) break;
+            if (ep.tile_group && ep.tile_group[mt] < 0) continue;
+            const int cur = it++, as = cur & 1;
+            if (!(ok = sq_wait(bar_tfull(as), (cur >> 1) & 1, abort_flag))) break;
             tc_fence_after();
             const int row = mt * SQ_BM + lg * 32 + lane;
             const uint32_t tacc = tmem_base + ((uint32_t)(lg * 32) << 16) + (uint32_t)(as * BN);
@@ -179,6 +191,35 @@ k_seq_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                                     if (ep.accumulate) o += dst[j];
                                     dst[j] = o;
                                 }
+                        }
+                    }
+                }
+            } else if (EPI == SQ_EPI_RELU2) {
+                const float wt = row < M ? ep.row_w[row] : 0.0f;
+#pragma unroll 1
+                for (int c = chalf * (BN / 64); c < (chalf + 1) * (BN / 64); c++) {
+                    const int col = nt * BN + c * 32;
+                    float v[32];
+                    tmem_ld32(tacc + (uint32_t)(c * 32), v);
+                    if (row < M && col < N) {
+                        __nv_bfloat16* dst = ep.act + (size_t)row * ep.ld_act + ep.act_off + col;
+                        const int nc = min(32, N - col);
+                        if (nc == 32 && ((((uintptr_t)dst) & 15) == 0)) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint32_t w[4];
+#pragma unroll
+                                for (int q = 0; q < 4; q++) {
+                                    const float a0 = fmaxf(v[j + 2 * q], 0.0f), a1 = fmaxf(v[j + 2 * q + 1], 0.0f);
+                                    const __nv_bfloat162 pr = __floats2bfloat162_rn(wt * a0 * a0, wt * a1 * a1);
+                                    w[q] = *reinterpret_cast<const uint32_t*>(&pr);
+                                }
+                                *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (j < nc) { const float a0 = fmaxf(v[j], 0.0f); dst[j] = __float2bfloat16_rn(wt * a0 * a0); }
                         }
                     }
                 }
@@ -231,7 +272,7 @@ typedef CUresult (*PFN_tmapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuin
 struct SeqGemmPlan {
     PFN_tmapEncodeTiled enc = nullptr;
     int* d_status = nullptr;
-    bool attr[2][2] = {{false, false}, {false, false}};
+    bool attr[2][3] = {{false, false, false}, {false, false, false}};
 };
 
 int seq_gemm_create(SeqGemmPlan** out) {
@@ -306,6 +347,23 @@ int seq_gemm_bf16(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw
     SqEpi ep{};
     ep.C = C; ep.ldc = ldc; ep.bias = bias; ep.accumulate = accumulate; ep.status = p ? p->d_status : nullptr;
     return run(p, SQ_EPI_F32, A, lda, W, ldw, M, N, K, ep);
+}
+
+int seq_gemm_bf16_grouped(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw, int M_pad, int N, int K, int n_groups, const int* tile_group,
+                          float* C, int ldc, void* act, int ld_act, const float* row_w) {
+    if (!p || K <= 0 || (K % SQ_BK) || (lda % 8) || (ldw % 8) || (((uintptr_t)A | (uintptr_t)W) & 15) || (M_pad % SQ_BM) || n_groups <= 0) return -1;
+    SqEpi ep{};
+    ep.C = C; ep.ldc = ldc; ep.act = reinterpret_cast<__nv_bfloat16*>(act); ep.ld_act = ld_act; ep.status = p->d_status;
+    ep.tile_group = tile_group; ep.group_rows = N; ep.row_w = row_w;
+    const int mt = M_pad / SQ_BM;
+    const int bn = (N > 128 && mt * ((N + 255) / 256) * 2 >= ctx().sm_count) ? 256 : 128;
+    CUtensorMap ta, tb;
+    int rc = make_map(p, &ta, A, M_pad, K, lda, SQ_BM);
+    if (rc) return rc;
+    rc = make_map(p, &tb, W, n_groups * N, K, ldw, bn);
+    if (rc) return rc;
+    if (act) return bn == 256 ? launch<256, SQ_EPI_RELU2>(p, ta, tb, M_pad, N, K, ep) : launch<128, SQ_EPI_RELU2>(p, ta, tb, M_pad, N, K, ep);
+    return bn == 256 ? launch<256, SQ_EPI_F32>(p, ta, tb, M_pad, N, K, ep) : launch<128, SQ_EPI_F32>(p, ta, tb, M_pad, N, K, ep);
 }
 
 int seq_gemm_bf16_geglu(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw, void* act, int ld_act, int act_off, int M, int N2, int K) {

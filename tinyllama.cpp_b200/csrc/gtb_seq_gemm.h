@@ -15,6 +15,11 @@ int seq_gemm_bf16(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw
 // fused feed-forward input: W holds gate rows and up rows interleaved in groups of 32 (N2 = 2 ff rows, a multiple of 64);
 // act[row][act_off + c] = bf16(gelu_tanh(gate_c) * up_c) -- the product never reaches HBM in fp32
 int seq_gemm_bf16_geglu(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw, void* act, int ld_act, int act_off, int M, int N2, int K);
+// grouped product for routed experts: A [M_pad][K] holds rows sorted into groups that start on multiples of 128 rows, tile_group
+// (device) [M_pad / 128] names every M tile's group or -1 (tile skipped, its output rows untouched); group g multiplies with rows
+// [g N, (g + 1) N) of W.  act != null: act[row][c] = bf16(row_w[row] * relu(.)^2) for c < N; else C[row][c] (fp32, ldc) is written
+int seq_gemm_bf16_grouped(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw, int M_pad, int N, int K, int n_groups, const int* tile_group,
+                          float* C, int ldc, void* act, int ld_act, const float* row_w);
 // 1 if a kernel of this plan gave up on a wait since the plan was created (its results are then not valid)
 int seq_gemm_status(SeqGemmPlan* p, int* status);
 

@@ -52,24 +52,36 @@ __global__ void __launch_bounds__(256) k_rmsnorm_weight(const float* __restrict_
 
 // Residual update of the post-norm style: y = Y (+ wid * x, the share of identity experts: pairs of sel_idx that are >= n_experts),
 // x += y / sqrt(mean(y^2) + eps) * (1 + w); the new stream is also written as the operand of the next matrix product.
+// Grouped experts: Y = null and the row's sublayer output is the sum of rows pair_dst[r * top + k] >= 0 of Yg (in order of k).
+constexpr int PN_MAX_TOP = 64;
 template <typename OT>
 __global__ void __launch_bounds__(256) k_postnorm_add(const float* __restrict__ Y, int width, float eps, const float* __restrict__ w,
                                                       const int* __restrict__ sel_idx, const float* __restrict__ sel_w, int top, int n_experts,
+                                                      const float* __restrict__ Yg, const int* __restrict__ pair_dst,
                                                       float* __restrict__ x, OT* __restrict__ op, int ld_op) {
     __shared__ float red[33];
+    __shared__ int sdst[PN_MAX_TOP];
     const int r = blockIdx.x;
     float wid = 0.0f;
     if (sel_idx)
         for (int k = 0; k < top; k++)
             if (sel_idx[(size_t)r * top + k] >= n_experts) wid += sel_w[(size_t)r * top + k];
-    const float* yr = Y + (size_t)r * width;
+    if (!Y && threadIdx.x < top) sdst[threadIdx.x] = pair_dst[(size_t)r * top + threadIdx.x];
+    __syncthreads();
+    auto sub = [&](int c) {
+        if (Y) return Y[(size_t)r * width + c];
+        float a = 0.0f;
+        for (int k = 0; k < top; k++)
+            if (sdst[k] >= 0) a += Yg[(size_t)sdst[k] * width + c];
+        return a;
+    };
     float* xr = x + (size_t)r * width;
     float ss = 0.0f;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = fmaf(wid, xr[c], yr[c]); ss += v * v; }
+    for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = fmaf(wid, xr[c], sub(c)); ss += v * v; }
     ss = block_sum(ss, red);
     const float sc = 1.0f / sqrtf(ss / (float)width + eps);
     for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        const float xo = xr[c], v = fmaf(wid, xo, yr[c]);
+        const float xo = xr[c], v = fmaf(wid, xo, sub(c));
         const float xn = xo + v * sc * (1.0f + w[c]);
         xr[c] = xn;
         op[(size_t)r * ld_op + c] = cvt<OT>(xn);
