@@ -105,6 +105,7 @@ struct gtb_seq_model {
     int attn_splits = 1;
     float* retU = nullptr;                       // chunked retention: per-chunk contributions / states [chunks][heads][dim][vdim]
     size_t retU_floats = 0;
+    float* sattn_part = nullptr;                 // split softmax attention: partial (max, denominator, values) [32][SPLIT_MAX_ROWS][heads][vdim + 2]
     float* gruAB = nullptr;                      // chunked minGRU: per-chunk maps [chunks][2][width]
     size_t gruAB_floats = 0;
     float* rl = nullptr;                         // router logits [max_rows][n_out_max]
@@ -339,6 +340,18 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         if (portions && sizeof(OT) == 2 && a.dim <= 128 && a.vdim <= 128)
             done = sattn_mma(t, a, S, n_qtiles, m->P, l.n1, (const bf16*)run.kc[0], (const bf16*)run.vc[0], run.pk, run.pv, (bf16*)opC, l.kout_p);
         if (done > 0) return done;
+        if (done < 0 && !portions && R <= SPLIT_MAX_ROWS && m->sattn_part) {
+            // decode rows: one CTA per 128 keys of the longest key list this layer can meet (window tokens + pooled blocks), at most 32
+            const int max_keys = a.window > 0 ? std::min(c.max_ctx, a.window + (a.pool > 0 ? c.max_ctx / a.pool : 0)) : c.max_ctx;
+            const int splits = std::max(1, std::min(32, (max_keys + 127) / 128));
+            if (splits > 1) {
+                k_sattn_split<OT><<<dim3(R, a.heads, splits), 128, (a.dim + 128 + 33) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[0], (const OT*)run.vc[0], run.pk, run.pv, m->sattn_part, R);
+                GTB_LAUNCHED();
+                k_sattn_join<OT><<<dim3(R, a.heads), 128, 0, st>>>(a, m->P, l.n1, m->sattn_part, R, splits, opC, l.kout_p);
+                GTB_LAUNCHED();
+                done = 0;
+            }
+        }
         if (done < 0) {
             k_sattn<OT><<<dim3(R, a.heads), 128, (a.dim + 128 + 33) * sizeof(float), st>>>(t, a, m->P, l.n1, (const OT*)run.kc[0], (const OT*)run.vc[0], run.pk, run.pv, opC, l.kout_p);
             GTB_LAUNCHED();
@@ -383,9 +396,12 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         }
     }
     if (E > 0) {
-        k_moe_up_rows<OT><<<dim3(R * top, std::max(1, std::min(8, (l.kfp + 7) / 8))), 256, 0, st>>>(opA, wp, wp, l.w_up, wp, l.ff, l.kfp, E, top, m->sel_idx, m->sel_w, (OT*)m->act);
+        // a warp per output column; with few (row, choice) pairs every column group gets its own CTA so that the experts' matrices stream at
+        // full width, with many pairs the grid is wide already
+        const int cta_budget = std::max(1, 4096 / std::max(1, R * top));
+        k_moe_up_rows<OT><<<dim3(R * top, std::max(1, std::min(cta_budget, (l.kfp + 7) / 8))), 256, 0, st>>>(opA, wp, wp, l.w_up, wp, l.ff, l.kfp, E, top, m->sel_idx, m->sel_w, (OT*)m->act);
         GTB_LAUNCHED();
-        k_moe_down_rows<OT><<<dim3(R, std::max(1, std::min(16, (W + 7) / 8))), 256, 0, st>>>((const OT*)m->act, l.kfp, l.w_down, W, E, top, m->sel_idx, m->Y, W);
+        k_moe_down_rows<OT><<<dim3(R, std::max(1, std::min(std::max(1, 4096 / R), (W + 7) / 8))), 256, 0, st>>>((const OT*)m->act, l.kfp, l.w_down, W, E, top, m->sel_idx, m->Y, W);
         GTB_LAUNCHED();
     } else {
         GTB_CUDA(cudaMemsetAsync(m->Y, 0, (size_t)R * W * sizeof(float), st));
@@ -846,6 +862,12 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     for (const LayerW& l : m->L)
         if (l.br[0].d.kind == GTB_MIX_MINGRU) m->gruAB_floats = std::max(m->gruAB_floats, (R / GRU_CHUNK + c.n_slots + 1) * 2 * (size_t)l.br[0].d.dim);
     if (m->gruAB_floats) TRY(dalloc_t(m, &m->gruAB, m->gruAB_floats));
+    {
+        size_t hv = 0;
+        for (const LayerW& l : m->L)
+            if (l.br[0].d.kind == GTB_MIX_SOFTMAX_ATTN) hv = std::max(hv, (size_t)l.br[0].d.heads * (l.br[0].d.vdim + 2));
+        if (hv > 0 && c.max_ctx > 128) TRY(dalloc_t(m, &m->sattn_part, 32 * SPLIT_MAX_ROWS * hv));
+    }
     if (m->n_out_max > 0) {
         TRY(dalloc_t(m, &m->rl, R * m->n_out_max));
         TRY(dalloc_t(m, &m->sel_idx, R * m->top_max));

@@ -293,21 +293,17 @@ __device__ __forceinline__ void sattn_range(const SoftAttn& b, int pos, int& lo,
     nb = (b.window > 0 && b.pool > 0 && pos - b.window + 1 >= b.pool) ? (pos - b.window + 1) / b.pool : 0;
 }
 
-// One CTA per (row, query head): online softmax over [pooled blocks | window tokens] in tiles of blockDim.x keys.  The running maximum
-// starts at the sink and the denominator at 1 (= exp(sink - sink)), so the sink counts once and no tile meets an empty history.
-// A thread scores one key of the tile, then the threads turn to the value channels.  vdim <= 4 * blockDim.x.
+// Online softmax of one (row, query head) over the keys n_lo .. n_hi-1 of the list [pooled blocks | window tokens], in tiles of
+// blockDim.x keys: a thread scores one key of the tile, then the threads turn to the value channels (vdim <= 4 * blockDim.x).
+// m, l: running maximum and denominator (in / out); acc: this thread's value channels.  sm: dim + blockDim.x + 33 floats.
 template <typename OT>
-__global__ void __launch_bounds__(128) k_sattn(PassTables t, SoftAttn b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc, const OT* __restrict__ vc,
-                                               const float* __restrict__ pk, const float* __restrict__ pv, OT* __restrict__ out, int ld_out) {
-    extern __shared__ float sm[];
+__device__ __forceinline__ void sattn_sweep(const PassTables& t, const SoftAttn& b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc,
+                                            const OT* __restrict__ vc, const float* __restrict__ pk, const float* __restrict__ pv, float* sm,
+                                            int r, int h, int n_lo, int n_hi, int lo, int nb, float& m, float& l, float (&acc)[4]) {
     float* sq = sm;                 // [dim]
     float* swt = sm + b.dim;        // [blockDim.x]
     float* red = swt + blockDim.x;  // [33]
-    const int r = blockIdx.x, h = blockIdx.y, g = h / (b.heads / b.kv_heads);
-    const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
-    int lo, nb;
-    sattn_range(b, pos, lo, nb);
-    const int total = nb + pos - lo + 1;
+    const int g = h / (b.heads / b.kv_heads), slot = t.seg_slot[t.row_seg[r]];
     const float* q = P + (size_t)r * ldp + b.q_off + h * b.dim;
     for (int i = threadIdx.x; i < b.dim; i += blockDim.x) sq[i] = q[i];
     const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
@@ -316,23 +312,21 @@ __global__ void __launch_bounds__(128) k_sattn(PassTables t, SoftAttn b, const f
     const float* pkb = pk ? pk + (size_t)slot * b.max_blocks * kld + (size_t)g * b.dim : nullptr;
     const float* pvb = pv ? pv + (size_t)slot * b.max_blocks * vld + (size_t)g * b.vdim : nullptr;
     const bool kvec = b.dim % 8 == 0;
-    float m = b.sink ? b.sink[h] : -INFINITY, l = b.sink ? 1.0f : 0.0f;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     __syncthreads();
-    for (int n0 = 0; n0 < total; n0 += blockDim.x) {
+    for (int n0 = n_lo; n0 < n_hi; n0 += blockDim.x) {
         const int n = n0 + threadIdx.x;
         float s = -INFINITY;
-        if (n < total) {
+        if (n < n_hi) {
             const float d = n < nb ? key_dot(sq, pkb + (size_t)n * kld, b.dim, b.dim % 4 == 0) : key_dot(sq, kbase + (size_t)(lo + n - nb) * kld, b.dim, kvec);
             s = soft_cap(d * b.scale, b.softcap);
         }
         const float mn = fmaxf(m, block_max(s, red));
-        const float corr = expf(m - mn);                 // m = -inf only before the first tile of a sink-less head: 0
-        const float pw = n < total ? expf(s - mn) : 0.0f;
+        const float corr = m == -INFINITY ? 0.0f : expf(m - mn);
+        const float pw = n < n_hi ? expf(s - mn) : 0.0f;
         swt[threadIdx.x] = pw;
         l = l * corr + block_sum(pw, red);               // (its barriers also publish swt)
         m = mn;
-        const int nj = min((int)blockDim.x, total - n0);
+        const int nj = min((int)blockDim.x, n_hi - n0);
 #pragma unroll
         for (int cc = 0; cc < 4; cc++) {
             const int c = threadIdx.x + cc * blockDim.x;
@@ -348,7 +342,10 @@ __global__ void __launch_bounds__(128) k_sattn(PassTables t, SoftAttn b, const f
         }
         __syncthreads();
     }
-    const float inv = 1.0f / l;
+}
+template <typename OT>
+__device__ __forceinline__ void sattn_store(const SoftAttn& b, const float* __restrict__ P, int ldp, int r, int h, float inv, const float (&acc)[4],
+                                            OT* __restrict__ out, int ld_out) {
 #pragma unroll
     for (int cc = 0; cc < 4; cc++) {
         const int c = threadIdx.x + cc * blockDim.x;
@@ -363,17 +360,85 @@ __global__ void __launch_bounds__(128) k_sattn(PassTables t, SoftAttn b, const f
     }
 }
 
+// One CTA per (row, query head) over all of the row's keys.  The running maximum starts at the sink and the denominator at 1
+// (= exp(sink - sink)), so the sink counts once and no tile meets an empty history.
+template <typename OT>
+__global__ void __launch_bounds__(128) k_sattn(PassTables t, SoftAttn b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc, const OT* __restrict__ vc,
+                                               const float* __restrict__ pk, const float* __restrict__ pv, OT* __restrict__ out, int ld_out) {
+    extern __shared__ float sm[];
+    const int r = blockIdx.x, h = blockIdx.y, pos = t.row_pos[r];
+    int lo, nb;
+    sattn_range(b, pos, lo, nb);
+    float m = b.sink ? b.sink[h] : -INFINITY, l = b.sink ? 1.0f : 0.0f;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    sattn_sweep<OT>(t, b, P, ldp, kc, vc, pk, pv, sm, r, h, 0, nb + pos - lo + 1, lo, nb, m, l, acc);
+    sattn_store<OT>(b, P, ldp, r, h, 1.0f / l, acc, out, ld_out);
+}
+
+// Decode rows: the keys of a (row, head) are split over gridDim.z CTAs in ranges of whole 128-key tiles; each leaves its running maximum,
+// denominator and unnormalised value sum in part [split][R][heads][vdim + 2] (an empty range: maximum -inf), k_sattn_join folds the splits
+// and the sink in order.
+template <typename OT>
+__global__ void __launch_bounds__(128) k_sattn_split(PassTables t, SoftAttn b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc,
+                                                     const OT* __restrict__ vc, const float* __restrict__ pk, const float* __restrict__ pv,
+                                                     float* __restrict__ part, int R) {
+    extern __shared__ float sm[];
+    const int r = blockIdx.x, h = blockIdx.y, pos = t.row_pos[r];
+    int lo, nb;
+    sattn_range(b, pos, lo, nb);
+    const int total = nb + pos - lo + 1;
+    const int per = ((total + (int)gridDim.z - 1) / (int)gridDim.z + 127) / 128 * 128;
+    const int n_lo = blockIdx.z * per, n_hi = min(total, n_lo + per);
+    float m = -INFINITY, l = 0.0f;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (n_lo < n_hi) sattn_sweep<OT>(t, b, P, ldp, kc, vc, pk, pv, sm, r, h, n_lo, n_hi, lo, nb, m, l, acc);
+    float* o = part + (((size_t)blockIdx.z * R + r) * b.heads + h) * (b.vdim + 2);
+    if (threadIdx.x == 0) { o[0] = m; o[1] = l; }
+#pragma unroll
+    for (int cc = 0; cc < 4; cc++) {
+        const int c = threadIdx.x + cc * blockDim.x;
+        if (c < b.vdim) o[2 + c] = acc[cc];
+    }
+}
+template <typename OT>
+__global__ void __launch_bounds__(128) k_sattn_join(SoftAttn b, const float* __restrict__ P, int ldp, const float* __restrict__ part, int R, int splits,
+                                                    OT* __restrict__ out, int ld_out) {
+    const int r = blockIdx.x, h = blockIdx.y;
+    const size_t stride = (size_t)R * b.heads * (b.vdim + 2);
+    const float* p0 = part + ((size_t)r * b.heads + h) * (b.vdim + 2);
+    float M = b.sink ? b.sink[h] : -INFINITY;
+    for (int k = 0; k < splits; k++) M = fmaxf(M, p0[k * stride]);
+    float l = b.sink ? expf(b.sink[h] - M) : 0.0f;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int k = 0; k < splits; k++) {
+        const float mk = p0[k * stride];
+        if (mk == -INFINITY) continue;
+        const float w = expf(mk - M);
+        l += p0[k * stride + 1] * w;
+#pragma unroll
+        for (int cc = 0; cc < 4; cc++) {
+            const int c = threadIdx.x + cc * blockDim.x;
+            if (c < b.vdim) acc[cc] = fmaf(p0[k * stride + 2 + c], w, acc[cc]);
+        }
+    }
+    sattn_store<OT>(b, P, ldp, r, h, 1.0f / l, acc, out, ld_out);
+}
+
 // ------------------------------------------------------------------------------------------------ PolyNorm
 // act = a N(z) + b N(z^2) + c N(z^3) + e, N(v) = v / sqrt(mean(v^2) + eps) over the row's ff values; coef = (a, b, c, e)
 template <typename OT>
 __global__ void __launch_bounds__(256) k_polynorm(const float* __restrict__ G, int ldg, int ff, float eps, const float* __restrict__ coef,
                                                   OT* __restrict__ out, int ld_out) {
-    __shared__ float red[33];
-    const int r = blockIdx.x;
+    __shared__ float red[3][9];
+    const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const float* z = G + (size_t)r * ldg;
     float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
     for (int c = threadIdx.x; c < ff; c += blockDim.x) { const float v = z[c], v2 = v * v; s2 += v2; s4 += v2 * v2; s6 += v2 * v2 * v2; }
-    s2 = block_sum(s2, red); s4 = block_sum(s4, red); s6 = block_sum(s6, red);
+    s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);         // the three sums share one pass and one barrier
+    if (lane == 0) { red[0][wid] = s2; red[1][wid] = s4; red[2][wid] = s6; }
+    __syncthreads();
+    s2 = s4 = s6 = 0.0f;
+    for (int w = 0; w < 8; w++) { s2 += red[0][w]; s4 += red[1][w]; s6 += red[2][w]; }
     const float n = (float)ff;
     const float k1 = coef[0] / sqrtf(s2 / n + eps), k2 = coef[1] / sqrtf(s4 / n + eps), k3 = coef[2] / sqrtf(s6 / n + eps), k0 = coef[3];
     for (int c = threadIdx.x; c < ff; c += blockDim.x) {
