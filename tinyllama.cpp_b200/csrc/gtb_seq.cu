@@ -169,7 +169,7 @@ void want_vector(gtb_seq_model* m, const std::string& name, float* dst, int rows
 size_t osz(const gtb_seq_model* m) { return m->cfg.mode == GTB_SEQ_F32 ? 4 : 2; }
 // fp32 values of recurrent state one slot holds for a branch
 size_t state_floats(const gtb_seq_branch& d) { return d.kind == GTB_MIX_MINGRU ? (size_t)d.dim : (size_t)d.heads * d.dim * d.vdim; }
-constexpr int GRU_CHUNK = 64;               // rows per chunk of the chunked minGRU scan
+constexpr int GRU_CHUNK = 32;               // rows per chunk of the chunked minGRU scan
 
 // C = (acc ? C : 0) + bias + A . W^T on the library stream; picks the tensor-core kernel, the few-row kernel or the SIMT tile kernel
 template <typename OT>

@@ -35,6 +35,13 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     return red[32];
 }
 
+// four consecutive operand elements at once (the destination is 8- or 16-byte aligned)
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) { *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d); }
+__device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float d) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    *reinterpret_cast<uint2*>(p) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
 // ------------------------------------------------------------------------------------------------ norms
 // out = x / sqrt(mean(x^2) + eps) * (one_plus + w[c]).  rows: optional gather (row index per output row).
 template <typename OUT>
@@ -53,7 +60,7 @@ __global__ void __launch_bounds__(256) k_rmsnorm_weight(const float* __restrict_
 // Residual update of the post-norm style: y = Y (+ wid * x, the share of identity experts: pairs of sel_idx that are >= n_experts),
 // x += y / sqrt(mean(y^2) + eps) * (1 + w); the new stream is also written as the operand of the next matrix product.
 // Grouped experts: Y = null and the row's sublayer output is the sum of rows pair_dst[r * top + k] >= 0 of Yg (in order of k).
-constexpr int PN_MAX_TOP = 64;
+constexpr int PN_MAX_TOP = 64, PN_KEEP = 4;
 template <typename OT>
 __global__ void __launch_bounds__(256) k_postnorm_add(const float* __restrict__ Y, int width, float eps, const float* __restrict__ w,
                                                       const int* __restrict__ sel_idx, const float* __restrict__ sel_w, int top, int n_experts,
@@ -77,6 +84,39 @@ __global__ void __launch_bounds__(256) k_postnorm_add(const float* __restrict__ 
     };
     float* xr = x + (size_t)r * width;
     float ss = 0.0f;
+    if (width % 4 == 0 && width <= 4 * PN_KEEP * (int)blockDim.x && ld_op % 4 == 0) {
+        // rows of up to 4 * PN_KEEP * blockDim.x values stay in registers between the two passes: every input is read once, 16 bytes at a time
+        float4 vx[PN_KEEP], vy[PN_KEEP];
+#pragma unroll
+        for (int i = 0; i < PN_KEEP; i++) {
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
+            if (c < width) {
+                vx[i] = *reinterpret_cast<const float4*>(xr + c);
+                float4 y = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (Y) y = *reinterpret_cast<const float4*>(Y + (size_t)r * width + c);
+                else
+                    for (int k = 0; k < top; k++)
+                        if (sdst[k] >= 0) { const float4 t4 = *reinterpret_cast<const float4*>(Yg + (size_t)sdst[k] * width + c); y.x += t4.x; y.y += t4.y; y.z += t4.z; y.w += t4.w; }
+                y.x = fmaf(wid, vx[i].x, y.x); y.y = fmaf(wid, vx[i].y, y.y); y.z = fmaf(wid, vx[i].z, y.z); y.w = fmaf(wid, vx[i].w, y.w);
+                vy[i] = y;
+                ss += y.x * y.x + y.y * y.y + y.z * y.z + y.w * y.w;
+            }
+        }
+        ss = block_sum(ss, red);
+        const float sc = 1.0f / sqrtf(ss / (float)width + eps);
+#pragma unroll
+        for (int i = 0; i < PN_KEEP; i++) {
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
+            if (c < width) {
+                const float4 g = *reinterpret_cast<const float4*>(w + c);
+                const float4 xn = make_float4(vx[i].x + vy[i].x * sc * (1.0f + g.x), vx[i].y + vy[i].y * sc * (1.0f + g.y),
+                                              vx[i].z + vy[i].z * sc * (1.0f + g.z), vx[i].w + vy[i].w * sc * (1.0f + g.w));
+                *reinterpret_cast<float4*>(xr + c) = xn;
+                store4(op + (size_t)r * ld_op + c, xn.x, xn.y, xn.z, xn.w);
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = fmaf(wid, xr[c], sub(c)); ss += v * v; }
     ss = block_sum(ss, red);
     const float sc = 1.0f / sqrtf(ss / (float)width + eps);
@@ -433,7 +473,23 @@ __global__ void __launch_bounds__(256) k_polynorm(const float* __restrict__ G, i
     const int r = blockIdx.x, lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const float* z = G + (size_t)r * ldg;
     float s2 = 0.0f, s4 = 0.0f, s6 = 0.0f;
-    for (int c = threadIdx.x; c < ff; c += blockDim.x) { const float v = z[c], v2 = v * v; s2 += v2; s4 += v2 * v2; s6 += v2 * v2 * v2; }
+    constexpr int KEEP = 8;
+    const bool keep = ff % 4 == 0 && ldg % 4 == 0 && ld_out % 4 == 0 && ff <= 4 * KEEP * (int)blockDim.x;     // the row stays in registers: read once
+    float4 vz[KEEP];
+    if (keep) {
+#pragma unroll
+        for (int i = 0; i < KEEP; i++) {
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
+            if (c < ff) {
+                const float4 v = *reinterpret_cast<const float4*>(z + c);
+                vz[i] = v;
+                const float a = v.x * v.x, b = v.y * v.y, cc = v.z * v.z, d = v.w * v.w;
+                s2 += a + b + cc + d; s4 += a * a + b * b + cc * cc + d * d; s6 += a * a * a + b * b * b + cc * cc * cc + d * d * d;
+            }
+        }
+    } else {
+        for (int c = threadIdx.x; c < ff; c += blockDim.x) { const float v = z[c], v2 = v * v; s2 += v2; s4 += v2 * v2; s6 += v2 * v2 * v2; }
+    }
     s2 = warp_sum(s2); s4 = warp_sum(s4); s6 = warp_sum(s6);         // the three sums share one pass and one barrier
     if (lane == 0) { red[0][wid] = s2; red[1][wid] = s4; red[2][wid] = s6; }
     __syncthreads();
@@ -441,6 +497,18 @@ __global__ void __launch_bounds__(256) k_polynorm(const float* __restrict__ G, i
     for (int w = 0; w < 8; w++) { s2 += red[0][w]; s4 += red[1][w]; s6 += red[2][w]; }
     const float n = (float)ff;
     const float k1 = coef[0] / sqrtf(s2 / n + eps), k2 = coef[1] / sqrtf(s4 / n + eps), k3 = coef[2] / sqrtf(s6 / n + eps), k0 = coef[3];
+    if (keep) {
+#pragma unroll
+        for (int i = 0; i < KEEP; i++) {
+            const int c = (threadIdx.x + i * blockDim.x) * 4;
+            if (c < ff) {
+                const float4 v = vz[i];
+                store4(out + (size_t)r * ld_out + c, fmaf(v.x, fmaf(v.x, fmaf(v.x, k3, k2), k1), k0), fmaf(v.y, fmaf(v.y, fmaf(v.y, k3, k2), k1), k0),
+                       fmaf(v.z, fmaf(v.z, fmaf(v.z, k3, k2), k1), k0), fmaf(v.w, fmaf(v.w, fmaf(v.w, k3, k2), k1), k0));
+            }
+        }
+        return;
+    }
     for (int c = threadIdx.x; c < ff; c += blockDim.x) {
         const float v = z[c];
         out[(size_t)r * ld_out + c] = cvt<OT>(fmaf(v, fmaf(v, fmaf(v, k3, k2), k1), k0));
