@@ -314,15 +314,26 @@ __global__ void __launch_bounds__(128) k_pool_update(PassTables t, SoftAttn b, c
     const OT* ks = kc + ((size_t)slot * b.max_ctx + (size_t)blk * b.pool) * kld;
     const OT* vs = vc + ((size_t)slot * b.max_ctx + (size_t)blk * b.pool) * vld;
     const float inv = 1.0f / (float)b.pool;
+    // four partial sums per element: four loads in flight instead of a chain of `pool` dependent ones
     for (int e = threadIdx.x; e < (int)kld; e += blockDim.x) {
-        float a = 0.0f;
-        for (int i = 0; i < b.pool; i++) a += ldf<OT>(ks + (size_t)i * kld + e);
-        pk[((size_t)slot * b.max_blocks + blk) * kld + e] = a * inv;
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        int i = 0;
+        for (; i + 3 < b.pool; i += 4) {
+            a0 += ldf<OT>(ks + (size_t)i * kld + e); a1 += ldf<OT>(ks + (size_t)(i + 1) * kld + e);
+            a2 += ldf<OT>(ks + (size_t)(i + 2) * kld + e); a3 += ldf<OT>(ks + (size_t)(i + 3) * kld + e);
+        }
+        for (; i < b.pool; i++) a0 += ldf<OT>(ks + (size_t)i * kld + e);
+        pk[((size_t)slot * b.max_blocks + blk) * kld + e] = ((a0 + a1) + (a2 + a3)) * inv;
     }
     for (int e = threadIdx.x; e < (int)vld; e += blockDim.x) {
-        float a = 0.0f;
-        for (int i = 0; i < b.pool; i++) a += ldf<OT>(vs + (size_t)i * vld + e);
-        pv[((size_t)slot * b.max_blocks + blk) * vld + e] = a * inv;
+        float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;
+        int i = 0;
+        for (; i + 3 < b.pool; i += 4) {
+            a0 += ldf<OT>(vs + (size_t)i * vld + e); a1 += ldf<OT>(vs + (size_t)(i + 1) * vld + e);
+            a2 += ldf<OT>(vs + (size_t)(i + 2) * vld + e); a3 += ldf<OT>(vs + (size_t)(i + 3) * vld + e);
+        }
+        for (; i < b.pool; i++) a0 += ldf<OT>(vs + (size_t)i * vld + e);
+        pv[((size_t)slot * b.max_blocks + blk) * vld + e] = ((a0 + a1) + (a2 + a3)) * inv;
     }
 }
 
