@@ -225,7 +225,7 @@ def robopel_section(torch, name, T, iters, warmup, peaks):
                 torch.cuda.synchronize()
                 t_ms.append(a.elapsed_time(b) / steps)
         ms = float(np.median(t_ms))
-        by = dec_bytes - 2 * desc["vocab"] * desc["width"]        # the embedding table is read one row per sequence
+        by = dec_bytes                                             # layers (top experts per routed layer) + head; the embedding is one row per sequence
         out[f"decode_{nseq}"] = {"ms_per_step": ms, "tokens_per_s": nseq / ms * 1e3, "bytes_per_step_one_sequence": by, "gbs": by / ms * 1e-6,
                                  "frac_of_hbm_peak": by / ms * 1e-6 / peaks["hbm_gbs"],
                                  "note": "bytes: weights one sequence's step reads (top experts per routed layer); further sequences add their experts and state"}
