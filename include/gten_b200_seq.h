@@ -67,6 +67,11 @@ typedef struct {
     int kv_from;                     /* -1: own keys and values */
 } gtb_seq_branch;
 
+/* Tensors of layer i beyond its branches'.  Parallel blocks: "l<i>.norm1" (one gain), "l<i>.mlp.{gate,up,down}", "l<i>.canon{1,2}".
+ * Post-norm layers: "l<i>.norm1", "l<i>.norm2" [width] (norm2 only with a feed-forward); GTB_FF_POLYNORM: "l<i>.mlp.up" [ff][width],
+ * "l<i>.mlp.down" [width][ff], "l<i>.mlp.act" [4]; GTB_FF_EXPERTS: "l<i>.mlp.router" [experts + identity][width], "l<i>.mlp.correction"
+ * [experts + identity], "l<i>.mlp.e<j>.up" [ff][width], "l<i>.mlp.e<j>.down" [width][ff].  A branch with an empty name has its tensors
+ * directly under "l<i>.mix.". */
 typedef struct {
     int n_branches;                  /* 1 or 2 */
     gtb_seq_branch branch[2];

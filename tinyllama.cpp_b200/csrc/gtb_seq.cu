@@ -359,7 +359,13 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
     }
     rc = product<OT>(m, opC, l.kout_p, l.w_out, l.kout_p, m->Y, W, R, W, l.kout_p, nullptr, 0);
     if (rc) return rc;
-    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm1, nullptr, nullptr, 0, 0, nullptr, nullptr, m->x, opA, wp);
+    // few rows and a routed feed-forward next: the residual update also computes the router's logits from the fp32 row it has just formed
+    // and picks the experts (two launches less per layer on a decode step)
+    RouteNext rn{};
+    const bool routed = l.ff > 0 && l.d.ff_kind == GTB_FF_EXPERTS;
+    const size_t rn_smem = routed ? ((size_t)W + 3 * l.n_out) * sizeof(float) : 0;
+    if (routed && R <= 8 && rn_smem <= 40 * 1024) { rn.w = l.w_router; rn.ldw = wp; rn.n_out = l.n_out; rn.top = l.d.top; rn.corr = l.d_corr; rn.sel_idx = m->sel_idx; rn.sel_w = m->sel_w; }
+    k_postnorm_add<OT><<<R, 256, rn.w ? rn_smem : 0, st>>>(m->Y, W, c.eps, l.norm1, nullptr, nullptr, 0, 0, nullptr, nullptr, m->x, opA, wp, rn);
     GTB_LAUNCHED();
     if (l.ff == 0) return GTB_OK;
     if (l.d.ff_kind == GTB_FF_POLYNORM) {
@@ -369,15 +375,17 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         GTB_LAUNCHED();
         rc = product<OT>(m, opC, l.kfp, l.w_down, l.kfp, m->Y, W, R, W, l.kfp, nullptr, 0);
         if (rc) return rc;
-        k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, nullptr, nullptr, 0, 0, nullptr, nullptr, m->x, opA, wp);
+        k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, nullptr, nullptr, 0, 0, nullptr, nullptr, m->x, opA, wp, RouteNext{});
         GTB_LAUNCHED();
         return GTB_OK;
     }
     const int E = l.d.experts, top = l.d.top;
-    rc = product<OT>(m, opA, wp, l.w_router, wp, m->rl, l.n_out, R, l.n_out, wp, nullptr, 0);
-    if (rc) return rc;
-    k_moe_route<<<R, 32, 2 * l.n_out * sizeof(float), st>>>(m->rl, l.n_out, l.n_out, l.d_corr, top, m->sel_idx, m->sel_w);
-    GTB_LAUNCHED();
+    if (!rn.w) {
+        rc = product<OT>(m, opA, wp, l.w_router, wp, m->rl, l.n_out, R, l.n_out, wp, nullptr, 0);
+        if (rc) return rc;
+        k_moe_route<<<R, 32, 2 * l.n_out * sizeof(float), st>>>(m->rl, l.n_out, l.n_out, l.d_corr, top, m->sel_idx, m->sel_w);
+        GTB_LAUNCHED();
+    }
     const int n_pairs = R * top, mpad = (n_pairs + 127) / 128 * 128 + E * 128;
     if (sizeof(OT) == 2 && E > 0 && m->grouped_experts && m->use_tensor && m->gp && m->Xg && R >= m->tensor_min_rows && mpad <= m->mpad_max) {
         // rows sorted by expert, two grouped tensor-core products (up with the weighted relu^2 epilogue, down), the choices of a row summed
@@ -390,7 +398,7 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         if (rc == 0) rc = seq_gemm_bf16_grouped(m->gp, m->actg, l.kfp, l.w_down, l.kfp, mpad, W, l.kfp, E, m->tile_e, m->Yg, W, nullptr, 0, nullptr);
         if (rc > 0) return rc;
         if (rc == 0) {
-            k_postnorm_add<OT><<<R, 256, 0, st>>>(nullptr, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, m->Yg, m->pair_dst, m->x, opA, wp);
+            k_postnorm_add<OT><<<R, 256, 0, st>>>(nullptr, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, m->Yg, m->pair_dst, m->x, opA, wp, RouteNext{});
             GTB_LAUNCHED();
             return GTB_OK;
         }
@@ -406,7 +414,7 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
     } else {
         GTB_CUDA(cudaMemsetAsync(m->Y, 0, (size_t)R * W * sizeof(float), st));
     }
-    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, nullptr, nullptr, m->x, opA, wp);
+    k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, nullptr, nullptr, m->x, opA, wp, RouteNext{});
     GTB_LAUNCHED();
     return GTB_OK;
 }
@@ -424,15 +432,15 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
     if (portions) for (int s = 0; s < S; s++) n_qtiles += (seg_lens[s] + 63) / 64;
     k_plan<<<(R + 127) / 128, 128, 0, st>>>(t, R, from_pending ? 1 : 0);
     GTB_LAUNCHED();
-    k_embed<<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, c.embed_scale != 0.0f ? c.embed_scale : 1.0f,
-                               m->x, c.loop_times > 0 ? m->x0 : nullptr);
+    const bool first_reads_x = m->L[m->runs[0].layer].d.style == GTB_BLOCK_POSTNORM;
+    k_embed<OT><<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, c.embed_scale != 0.0f ? c.embed_scale : 1.0f,
+                                   m->x, c.loop_times > 0 ? m->x0 : nullptr, first_reads_x ? opA : (OT*)nullptr, wp);
     GTB_LAUNCHED();
-    bool x_in_opA = false;
+    bool x_in_opA = first_reads_x;
     for (size_t u = 0; u < m->runs.size(); u++) {
         const Run& run = m->runs[u];
         const LayerW& l = m->L[run.layer];
         if (l.d.style == GTB_BLOCK_POSTNORM) {
-            if (run.enters_pass) return gtb::fail(GTB_ERR_STATE, "a post-norm layer cannot open a loop pass");
             int rc = run_postnorm_layer<OT>(m, t, R, S, run, l, portions, seg_lens, n_qtiles, x_in_opA);
             if (rc) return rc;
             x_in_opA = true;
@@ -805,6 +813,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     } else {
         for (int i = 0; i < c.n_layers; i++) add_run(i, -1, false);
     }
+    for (const Run& r : m->runs) REQ(!(r.enters_pass && m->L[r.layer].d.style == GTB_BLOCK_POSTNORM));      // a loop pass opens with a parallel block
     // state of every run, for every slot
     const size_t es = osz(m);
     for (Run& r : m->runs) {

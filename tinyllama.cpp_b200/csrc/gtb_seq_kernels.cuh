@@ -124,9 +124,11 @@ __global__ void k_commit(PassTables t, int S) {
 }
 
 // ------------------------------------------------------------------------------------------------ embedding
-// x = scale * embed[tok] (+ bigram[(prev * mul_prev + tok * mul_cur) mod buckets], row `buckets` for a sequence's first token); x0 = x
+// x = scale * embed[tok] (+ bigram[(prev * mul_prev + tok * mul_cur) mod buckets], row `buckets` for a sequence's first token); x0 = x;
+// op (optional): x again as the operand of the first matrix product, for models whose first layer reads the stream itself
+template <typename OT>
 __global__ void k_embed(PassTables t, const bf16* __restrict__ embed, const bf16* __restrict__ bigram, int buckets, int mul_prev,
-                        int mul_cur, int width, float scale, float* __restrict__ x, float* __restrict__ x0) {
+                        int mul_cur, int width, float scale, float* __restrict__ x, float* __restrict__ x0, OT* __restrict__ op, int ld_op) {
     const int r = blockIdx.x;
     const int tok = t.tok[r], prev = t.row_prev[r];
     long long row = buckets;
@@ -136,6 +138,7 @@ __global__ void k_embed(PassTables t, const bf16* __restrict__ embed, const bf16
         if (buckets > 0) v += __bfloat162float(bigram[(size_t)row * width + c]);
         x[(size_t)r * width + c] = v;
         if (x0) x0[(size_t)r * width + c] = v;
+        if (op) op[(size_t)r * ld_op + c] = cvt<OT>(v);
     }
 }
 

@@ -57,6 +57,77 @@ __global__ void __launch_bounds__(256) k_rmsnorm_weight(const float* __restrict_
     for (int c = threadIdx.x; c < width; c += blockDim.x) out[(size_t)o * ld_out + c] = cvt<OUT>(xr[c] * sc * (base + w[c]));
 }
 
+// ------------------------------------------------------------------------------------------------ router
+// One warp routes one row: s = softmax(z) over all n_out router outputs; the `top` outputs with the largest s + corr are chosen (ties to
+// the lower index); sel_w holds their s (not renormalised).  s, ch: n_out floats of shared memory each.
+__device__ __forceinline__ void route_row(const float* __restrict__ z, int n_out, const float* __restrict__ corr, int top, int* __restrict__ sel_idx,
+                                          float* __restrict__ sel_w, float* s, float* ch, int lane) {
+    float mx = -INFINITY;
+    for (int i = lane; i < n_out; i += 32) mx = fmaxf(mx, z[i]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int i = lane; i < n_out; i += 32) { const float e = expf(z[i] - mx); s[i] = e; sum += e; }
+    sum = warp_sum(sum);
+    const float inv = 1.0f / sum;
+    for (int i = lane; i < n_out; i += 32) { const float v = s[i] * inv; s[i] = v; ch[i] = v + (corr ? corr[i] : 0.0f); }
+    __syncwarp();
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int arg = 0x7fffffff;
+        for (int i = lane; i < n_out; i += 32) { const float v = ch[i]; if (v > best) { best = v; arg = i; } }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
+            if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
+        }
+        if (arg == 0x7fffffff) arg = 0;                  // every remaining choice score is -inf or NaN
+        if (lane == 0) { sel_idx[k] = arg; sel_w[k] = s[arg]; ch[arg] = -INFINITY; }
+        __syncwarp();
+    }
+}
+// rows of router logits Z -> choices; shared memory: 2 n_out floats
+__global__ void __launch_bounds__(32) k_moe_route(const float* __restrict__ Z, int ldz, int n_out, const float* __restrict__ corr, int top,
+                                                  int* __restrict__ sel_idx, float* __restrict__ sel_w) {
+    extern __shared__ float sm[];
+    const int r = blockIdx.x;
+    route_row(Z + (size_t)r * ldz, n_out, corr, top, sel_idx + (size_t)r * top, sel_w + (size_t)r * top, sm, sm + n_out, threadIdx.x);
+}
+// The router of the NEXT sublayer inside the residual update (few rows): what k_postnorm_add appends when it is given a router
+struct RouteNext {
+    const bf16* w;             // [n_out][ldw] router matrix, or null: no routing here
+    int ldw, n_out, top;
+    const float* corr;
+    int* sel_idx;              // [rows][top]
+    float* sel_w;
+};
+
+// router logits of row r from its new stream values sx [width] (fp32, shared memory) -- a warp per output -- and the row's choices
+__device__ __forceinline__ void postnorm_route(const RouteNext& rn, float* sx, int width, int r) {
+    float* sl = sx + width;              // [n_out] logits, then [n_out] scores and [n_out] choice scores
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = blockDim.x >> 5;
+    __syncthreads();
+    for (int j = wid; j < rn.n_out; j += nw) {
+        const bf16* wr = rn.w + (size_t)j * rn.ldw;
+        float a = 0.0f;
+        const int w8 = width & ~7;                   // rows of the router matrix start on 16-byte boundaries: eight weights per load
+        for (int c = lane * 8; c < w8; c += 256) {
+            const uint4 wv = __ldg(reinterpret_cast<const uint4*>(wr + c));
+            const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                a = fmaf(sx[c + 2 * i], __uint_as_float(ww[i] << 16), a);
+                a = fmaf(sx[c + 2 * i + 1], __uint_as_float(ww[i] & 0xffff0000u), a);
+            }
+        }
+        for (int c = w8 + lane; c < width; c += 32) a = fmaf(sx[c], __bfloat162float(wr[c]), a);
+        a = warp_sum(a);
+        if (lane == 0) sl[j] = a;
+    }
+    __syncthreads();
+    if (wid == 0) route_row(sl, rn.n_out, rn.corr, rn.top, rn.sel_idx + (size_t)r * rn.top, rn.sel_w + (size_t)r * rn.top, sl + rn.n_out, sl + 2 * rn.n_out, lane);
+}
+
 // Residual update of the post-norm style: y = Y (+ wid * x, the share of identity experts: pairs of sel_idx that are >= n_experts),
 // x += y / sqrt(mean(y^2) + eps) * (1 + w); the new stream is also written as the operand of the next matrix product.
 // Grouped experts: Y = null and the row's sublayer output is the sum of rows pair_dst[r * top + k] >= 0 of Yg (in order of k).
@@ -65,9 +136,10 @@ template <typename OT>
 __global__ void __launch_bounds__(256) k_postnorm_add(const float* __restrict__ Y, int width, float eps, const float* __restrict__ w,
                                                       const int* __restrict__ sel_idx, const float* __restrict__ sel_w, int top, int n_experts,
                                                       const float* __restrict__ Yg, const int* __restrict__ pair_dst,
-                                                      float* __restrict__ x, OT* __restrict__ op, int ld_op) {
+                                                      float* __restrict__ x, OT* __restrict__ op, int ld_op, RouteNext rn) {
     __shared__ float red[33];
     __shared__ int sdst[PN_MAX_TOP];
+    extern __shared__ float srt[];       // routing: the new stream row [width], logits [n_out], two work arrays [n_out]
     const int r = blockIdx.x;
     float wid = 0.0f;
     if (sel_idx)
@@ -113,8 +185,10 @@ __global__ void __launch_bounds__(256) k_postnorm_add(const float* __restrict__ 
                                               vx[i].z + vy[i].z * sc * (1.0f + g.z), vx[i].w + vy[i].w * sc * (1.0f + g.w));
                 *reinterpret_cast<float4*>(xr + c) = xn;
                 store4(op + (size_t)r * ld_op + c, xn.x, xn.y, xn.z, xn.w);
+                if (rn.w) { srt[c] = xn.x; srt[c + 1] = xn.y; srt[c + 2] = xn.z; srt[c + 3] = xn.w; }
             }
         }
+        if (rn.w) postnorm_route(rn, srt, width, r);
         return;
     }
     for (int c = threadIdx.x; c < width; c += blockDim.x) { const float v = fmaf(wid, xr[c], sub(c)); ss += v * v; }
@@ -125,7 +199,9 @@ __global__ void __launch_bounds__(256) k_postnorm_add(const float* __restrict__ 
         const float xn = xo + v * sc * (1.0f + w[c]);
         xr[c] = xn;
         op[(size_t)r * ld_op + c] = cvt<OT>(xn);
+        if (rn.w) srt[c] = xn;
     }
+    if (rn.w) postnorm_route(rn, srt, width, r);
 }
 
 // ------------------------------------------------------------------------------------------------ minGRU
@@ -527,40 +603,6 @@ __global__ void __launch_bounds__(256) k_polynorm(const float* __restrict__ G, i
 }
 
 // ------------------------------------------------------------------------------------------------ routed experts
-// One warp per row: s = softmax(Z) over all n_out router outputs; the `top` outputs with the largest s + corr are chosen (ties to the
-// lower index); sel_w holds their s (not renormalised).  Shared memory: 2 n_out floats.
-__global__ void __launch_bounds__(32) k_moe_route(const float* __restrict__ Z, int ldz, int n_out, const float* __restrict__ corr, int top,
-                                                  int* __restrict__ sel_idx, float* __restrict__ sel_w) {
-    extern __shared__ float sm[];
-    float* s = sm;
-    float* ch = sm + n_out;
-    const int r = blockIdx.x, lane = threadIdx.x;
-    const float* z = Z + (size_t)r * ldz;
-    float mx = -INFINITY;
-    for (int i = lane; i < n_out; i += 32) mx = fmaxf(mx, z[i]);
-    mx = warp_max(mx);
-    float sum = 0.0f;
-    for (int i = lane; i < n_out; i += 32) { const float e = expf(z[i] - mx); s[i] = e; sum += e; }
-    sum = warp_sum(sum);
-    const float inv = 1.0f / sum;
-    for (int i = lane; i < n_out; i += 32) { const float v = s[i] * inv; s[i] = v; ch[i] = v + (corr ? corr[i] : 0.0f); }
-    __syncwarp();
-    for (int k = 0; k < top; k++) {
-        float best = -INFINITY;
-        int arg = 0x7fffffff;
-        for (int i = lane; i < n_out; i += 32) { const float v = ch[i]; if (v > best) { best = v; arg = i; } }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, arg, o);
-            if (ov > best || (ov == best && oi < arg)) { best = ov; arg = oi; }
-        }
-        if (arg == 0x7fffffff) arg = 0;                  // every remaining choice score is -inf or NaN
-        if (lane == 0) { sel_idx[(size_t)r * top + k] = arg; sel_w[(size_t)r * top + k] = s[arg]; ch[arg] = -INFINITY; }
-        __syncwarp();
-    }
-}
-
 // lane-partial dot of an operand row with a bf16 weight row over K (a multiple of 64; both rows 16-byte aligned)
 template <typename OT>
 __device__ __forceinline__ float lane_dot(const OT* __restrict__ a, const bf16* __restrict__ w, int K, int lane) {
