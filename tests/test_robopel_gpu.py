@@ -434,11 +434,14 @@ def test_router_choice_uses_the_correction_and_weights_do_not(lib):
         t["l0.mlp.correction"] = st.f32_to_bf16_bits(c)
     m, W = make(lib, cfg, "float32", seed=71, tweak=tweak)
     t = toks(7, 30, 40)
-    x = R.forward(cfg, W, t)[1]
     pick, w = R.route(np.random.default_rng(0).standard_normal((6, 32)), W["l0.mlp.router"], W["l0.mlp.correction"], 2)
-    assert np.all(pick[:, 0] == 3) and np.all(w[:, 0] < 0.9)
-    assert rel(m.step([(0, t)], range(30)), R.forward(cfg, W, t)[0]) < TOL["float32"]
-    assert x.shape == (1, 30, 32)
+    assert np.all(pick[:, 0] == 3) and np.all(w[:, 0] < 0.9)          # the restatement: expert 3 always comes first, with a score of its own size
+    want = R.forward(cfg, W, t)[0]
+    assert rel(m.step([(0, t)], range(30)), want) < TOL["float32"]                                             # whole prompt: router product + routing kernel
+    assert rel(np.concatenate([m.step([(1, t[i:i + 1])], [0]) for i in range(30)]), want) < TOL["float32"]      # row by row: routing inside the residual update
+    plain = dict(W)
+    plain["l0.mlp.correction"] = np.zeros(5)
+    assert rel(R.forward(cfg, plain, t)[0], want) > 50 * TOL["float32"]                                        # and the correction matters
 
 
 # ------------------------------------------------------------------ generation through the scheduler, command line
