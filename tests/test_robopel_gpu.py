@@ -379,7 +379,7 @@ def test_other_sizes(lib, layers, vocab, width):
 @pytest.mark.parametrize("layers", [
     [A(heads=4, kv_heads=2, dim=16, vdim=16, window=40, pool=8, rot_dims=16, mlp=E(6, 2, 2, 32)), G(width=48, mlp=D(64))],
     [A(heads=2, kv_heads=1, dim=48, vdim=40, window=100, pool=16, rot_dims=24), A(heads=4, kv_heads=1, dim=48, vdim=40, window=70, pool=5, rot_dims=48, kv_from=0, mlp=E(3, 1, 2, 24))],
-    [A(heads=3, kv_heads=3, dim=20, vdim=12, window=64, pool=64, rot_dims=8), G(width=136, mlp=E(16, 2, 2, 96))],
+    [A(heads=3, kv_heads=3, dim=20, vdim=12, window=64, pool=64, rot_dims=8), G(width=136, mlp=E(12, 3, 2, 80))],
     [A(heads=2, kv_heads=2, dim=128, vdim=128, window=0, pool=0, rot_dims=128, softcap=0), A(heads=2, kv_heads=2, dim=64, vdim=64, window=128, pool=32, mlp=D(128))],
 ])
 def test_tiled_kernels_on_portions(lib, mode, layers):
